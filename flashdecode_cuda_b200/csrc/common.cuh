@@ -1,0 +1,81 @@
+// Shared device helpers for the sm_100a kernels of this library.
+//
+// Conventions used by every kernel file:
+//  * activations and weights are `float` (true 32-bit path) or `__nv_bfloat16`
+//    (serving path); every reduction, softmax, norm and rotation is done in
+//    float and rounded once on store;
+//  * every launcher is `extern "C"`, takes raw device pointers and a stream,
+//    launches without allocating, and returns 0 or a negative error code whose
+//    text `fd_last_error()` gives;
+//  * kernels that index through tables (token ids, block tables) check the
+//    index and, instead of faulting, skip the access and set a bit in a status
+//    word that the host reads at its next synchronisation.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fd {
+
+// status bits written by kernels (host: flashdecode_cuda_b200/kernels.py)
+constexpr int STATUS_BAD_TOKEN = 1;       // token id outside the embedding table
+constexpr int STATUS_BAD_BLOCK = 2;       // block table entry < 0 or >= num_blocks where a token lies
+constexpr int STATUS_BAD_POSITION = 4;    // position beyond the rotation table
+constexpr int STATUS_WAIT_TIMEOUT = 8;    // a bounded mbarrier wait gave up
+
+__device__ __forceinline__ void set_status(int* status, int bit) {
+    if (status != nullptr) atomicOr(status, bit);
+}
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a thread block; every thread gets the result.  `scratch` holds at
+// least 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    const float total = scratch[32];
+    __syncthreads();
+    return total;
+}
+
+}  // namespace fd
+
+// error reporting shared by the launchers (defined in runtime.cu)
+extern "C" const char* fd_last_error();
+namespace fd {
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what);
+}  // namespace fd
+
+#define FD_REQUIRE(cond, code, ...) \
+    do { if (!(cond)) return fd::fail(code, __VA_ARGS__); } while (0)

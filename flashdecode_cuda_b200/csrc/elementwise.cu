@@ -1,0 +1,240 @@
+// Row-wise kernels: embedding gather, fused residual-add + RMSNorm, SiLU*up,
+// and rotary position encoding fused with the append to the paged KV cache.
+//
+// All of them are bound by memory traffic or launch latency; each does its
+// arithmetic in float and rounds once on store.
+#include "common.cuh"
+
+namespace fd {
+
+// ---------------------------------------------------------------------------
+// embedding: resid[t, :] = float(table[token[t], :])
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             float* __restrict__ resid, int H, int V, int* status) {
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    float* dst = resid + (size_t)t * H;
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) set_status(status, STATUS_BAD_TOKEN);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = 0.f;
+        return;
+    }
+    const TW* src = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+// ---------------------------------------------------------------------------
+// residual add + RMSNorm.  For output row j (source row r = rows ? rows[j] : j):
+//   x = resid[r] + sum_p delta[p][r]        (float; parts added in index order)
+//   resid[r] = x                             (if write_resid)
+//   out[j] = x * rsqrt(mean(x^2) + eps) * w  (float, rounded once)
+// `delta` may be null (plain norm).  Several parts are the partial sums a
+// split-K matrix product leaves behind.
+// ---------------------------------------------------------------------------
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, int n_parts, size_t part_stride,
+                                   float* __restrict__ resid, int write_resid,
+                                   const TW* __restrict__ w, float eps, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int H) {
+    extern __shared__ float smem[];
+    float* xs = smem;                 // H floats
+    float* red = smem + ((H + 3) & ~3);  // 33 floats
+    const int j = blockIdx.x;
+    const int r = rows ? rows[j] : j;
+    float* rrow = resid + (size_t)r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float x = rrow[i];
+        if (delta != nullptr) {
+            for (int p = 0; p < n_parts; ++p) x += to_float(delta[p * part_stride + (size_t)r * H + i]);
+            if (write_resid) rrow[i] = x;
+        }
+        xs[i] = x;
+        ss += x * x;
+    }
+    const float total = block_sum(ss, red);
+    const float rstd = rsqrtf(total / (float)H + eps);
+    TO* orow = out + (size_t)j * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        orow[i] = from_float<TO>(xs[i] * rstd * to_float(w[i]));
+}
+
+// ---------------------------------------------------------------------------
+// out[m, i] = silu(gu[m, i]) * gu[m, I + i]
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; e < total; e += stride) {
+        const size_t m = e / I;
+        const int i = (int)(e - m * I);
+        const float g = to_float(gu[m * 2 * I + i]);
+        const float u = to_float(gu[m * 2 * I + I + i]);
+        out[e] = from_float<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// rotary encoding (rotate-half pairing: j with j + d/2) of q and k, and the
+// append of the rotated k and of v to the paged cache at the token's position.
+//   qkv  [T, (n_q + 2 n_kv) d]   rows: q heads, then k heads, then v heads
+//   q_out[T, n_q d]
+//   pools [num_blocks, n_kv, block_size, d]
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                   int table_len, const int* __restrict__ tok_row,
+                                   const int* __restrict__ tok_pos, const int* __restrict__ row_slot,
+                                   T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                   const int* __restrict__ block_table, int max_blocks, int num_blocks,
+                                   int block_size, int n_q, int n_kv, int d, int write_kv, int* status) {
+    const int t = blockIdx.x;
+    const int half = d >> 1;
+    const int slot = row_slot[tok_row[t]];
+    if (slot < 0) return;             // padding row of a fixed-size batch: nothing to do
+    int pos = tok_pos[t];
+    bool pos_ok = pos >= 0 && pos < table_len;
+    if (!pos_ok) {
+        if (threadIdx.x == 0) set_status(status, STATUS_BAD_POSITION);
+        pos = 0;
+    }
+    const float* c = cos_t + (size_t)pos * half;
+    const float* s = sin_t + (size_t)pos * half;
+    const T* row = qkv + (size_t)t * (n_q + 2 * n_kv) * d;
+
+    // destination of this token's keys and values
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (write_kv && pos_ok) {
+        const int blk = block_table[(size_t)slot * max_blocks + pos / block_size];
+        if (blk < 0 || blk >= num_blocks) {
+            if (threadIdx.x == 0) set_status(status, STATUS_BAD_BLOCK);
+        } else {
+            const size_t base = ((size_t)blk * n_kv * block_size + (pos % block_size)) * d;
+            kdst = k_pool + base;
+            vdst = v_pool + base;
+        }
+    }
+    const size_t head_stride = (size_t)block_size * d;   // between kv heads inside a block
+
+    const int n_rot = (n_q + n_kv) * half;
+    for (int e = threadIdx.x; e < n_rot; e += blockDim.x) {
+        const int h = e / half, j = e - h * half;
+        const float x1 = to_float(row[h * d + j]);
+        const float x2 = to_float(row[h * d + j + half]);
+        const float cj = c[j], sj = s[j];
+        const T y1 = from_float<T>(x1 * cj - x2 * sj);
+        const T y2 = from_float<T>(x2 * cj + x1 * sj);
+        if (h < n_q) {
+            T* o = q_out + ((size_t)t * n_q + h) * d;
+            o[j] = y1;
+            o[j + half] = y2;
+        } else if (kdst != nullptr) {
+            T* o = kdst + (h - n_q) * head_stride;
+            o[j] = y1;
+            o[j + half] = y2;
+        }
+    }
+    if (vdst != nullptr) {
+        const T* vrow = row + (size_t)(n_q + n_kv) * d;
+        for (int e = threadIdx.x; e < n_kv * d; e += blockDim.x) {
+            const int h = e / d, j = e - h * d;
+            vdst[h * head_stride + j] = vrow[e];
+        }
+    }
+}
+
+}  // namespace fd
+
+using namespace fd;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int fd_embed(const int* tokens, const void* table, int table_dtype, float* resid,
+                        int T, int H, int V, int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    FD_REQUIRE(H > 0 && V > 0, -2, "embed: bad sizes H=%d V=%d", H, V);
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == 0)
+        embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, resid, H, V, status);
+    else
+        embed_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, resid, H, V, status);
+    return check_launch("embed");
+}
+
+template <typename TD, typename TO>
+static int launch_norm(const void* delta, int n_parts, size_t part_stride, float* resid, int write_resid,
+                       const void* w, int w_dtype, float eps, void* out, const int* rows, int n_out, int H,
+                       cudaStream_t stream) {
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const size_t smem = (((H + 3) & ~3) + 40) * sizeof(float);
+    FD_REQUIRE(smem <= 200 * 1024, -2, "add_rmsnorm: width %d needs %zu bytes of shared memory (max 200 KB)", H, smem);
+    if (w_dtype == 0) {
+        auto k = add_rmsnorm_kernel<TD, float, TO>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<n_out, threads, smem, stream>>>((const TD*)delta, n_parts, part_stride, resid, write_resid,
+                                            (const float*)w, eps, (TO*)out, rows, H);
+    } else {
+        auto k = add_rmsnorm_kernel<TD, bf16, TO>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<n_out, threads, smem, stream>>>((const TD*)delta, n_parts, part_stride, resid, write_resid,
+                                            (const bf16*)w, eps, (TO*)out, rows, H);
+    }
+    return check_launch("add_rmsnorm");
+}
+
+// delta_dtype / w_dtype / out_dtype: 0 = float32, 1 = bfloat16.
+extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, long long part_stride,
+                              float* resid, int write_resid, const void* weight, int w_dtype, float eps,
+                              void* out, int out_dtype, const int* rows, int n_out, int H,
+                              cudaStream_t stream) {
+    if (n_out == 0) return 0;
+    FD_REQUIRE(H > 0, -2, "add_rmsnorm: bad width %d", H);
+    FD_REQUIRE(delta == nullptr || n_parts >= 1, -2, "add_rmsnorm: n_parts=%d", n_parts);
+    const size_t ps = (size_t)part_stride;
+    if (delta_dtype == 0 && out_dtype == 0)
+        return launch_norm<float, float>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);
+    if (delta_dtype == 1 && out_dtype == 1)
+        return launch_norm<bf16, bf16>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);
+    if (delta_dtype == 0 && out_dtype == 1)
+        return launch_norm<float, bf16>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);
+    return fail(-2, "add_rmsnorm: unsupported dtypes delta=%d out=%d", delta_dtype, out_dtype);
+}
+
+extern "C" int fd_silu_mul(const void* gu, void* out, int dtype, int M, int I, cudaStream_t stream) {
+    const size_t total = (size_t)M * I;
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == 0)
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    else
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+    return check_launch("silu_mul");
+}
+
+extern "C" int fd_rope_append(const void* qkv, void* q_out, int dtype, const float* cos_t, const float* sin_t,
+                              int table_len, const int* tok_row, const int* tok_pos, const int* row_slot,
+                              void* k_pool, void* v_pool, const int* block_table, int max_blocks,
+                              int num_blocks, int block_size, int T, int n_q, int n_kv, int d, int write_kv,
+                              int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    FD_REQUIRE(d > 0 && d % 2 == 0, -2, "rope_append: head size %d must be even", d);
+    FD_REQUIRE(block_size > 0 && n_q > 0 && n_kv > 0, -2, "rope_append: bad sizes");
+    const int work = (n_q + n_kv) * d / 2;
+    const int threads = work >= 512 ? 256 : 128;
+    if (dtype == 0)
+        rope_append_kernel<float><<<T, threads, 0, stream>>>(
+            (const float*)qkv, (float*)q_out, cos_t, sin_t, table_len, tok_row, tok_pos, row_slot,
+            (float*)k_pool, (float*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv, d,
+            write_kv, status);
+    else
+        rope_append_kernel<bf16><<<T, threads, 0, stream>>>(
+            (const bf16*)qkv, (bf16*)q_out, cos_t, sin_t, table_len, tok_row, tok_pos, row_slot,
+            (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv, d,
+            write_kv, status);
+    return check_launch("rope_append");
+}

@@ -1,0 +1,46 @@
+// Error reporting and device queries shared by all launchers.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+extern "C" const char* fd_last_error() { return g_error; }
+
+namespace fd {
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+}  // namespace fd
+
+// Compute capability of the current device as major*10+minor, or a negative
+// error code.  The package refuses to run on anything but 10.x.
+extern "C" int fd_device_arch() {
+    int dev = 0, major = 0, minor = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fd::fail(-1, "no CUDA device");
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    return major * 10 + minor;
+}
+
+extern "C" int fd_sm_count() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return fd::fail(-1, "no CUDA device");
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+}

@@ -1,0 +1,105 @@
+// Token choice from float logits: greedy (argmax, lowest index wins a tie) or
+// temperature sampling by the Gumbel-max rule,
+//     token = argmax_i ( logit_i / T + g_i ),   g_i = -log(-log(u_i)),
+// which draws exactly from softmax(logits / T) without a prefix sum.  The
+// uniform u_i = ((x_i >> 9) + 0.5) / 2^23 (exact in float, never 0 or 1) comes from Philox-4x32-10 with counter (i / 4, step, request)
+// and key (seed): a draw depends on the request, its step and the vocabulary
+// index only, never on which other rows share the batch.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace fd {
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                              uint32_t k0, uint32_t k1, uint32_t out[4]) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+    return v > bv || (v == bv && i < bi);
+}
+
+// One CTA per row.  temperature[row] <= 0 means greedy.
+__global__ void __launch_bounds__(512)
+sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+              const long long* __restrict__ request, const int* __restrict__ step,
+              unsigned long long seed, int* __restrict__ out) {
+    const int row = blockIdx.x;
+    const float* x = logits + (size_t)row * V;
+    const float temp = temperature ? temperature[row] : 0.f;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    if (temp <= 0.f) {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = x[i];
+            if (better(v, i, bv, bi)) { bv = v; bi = i; }
+        }
+    } else {
+        const unsigned long long rq = (unsigned long long)request[row];
+        const uint32_t st = (uint32_t)step[row];
+        const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+        for (int j = threadIdx.x; j * 4 < V; j += blockDim.x) {
+            uint32_t r[4];
+            philox4x32_10((uint32_t)j, st, (uint32_t)rq, (uint32_t)(rq >> 32), k0, k1, r);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = j * 4 + e;
+                if (i < V) {
+                    const float u = ((float)(r[e] >> 9) + 0.5f) * (1.0f / 8388608.0f);
+                    const float v = x[i] / temp + (-logf(-logf(u)));
+                    if (better(v, i, bv, bi)) { bv = v; bi = i; }
+                }
+            }
+        }
+    }
+    // block argmax
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        bv = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+}  // namespace fd
+
+using namespace fd;
+
+// logits [n, V] float; temperature [n] float or null (all greedy); request [n]
+// int64 and step [n] int32 (needed when any temperature is > 0); out [n] int32.
+extern "C" int fd_sample(const float* logits, int n, int V, const float* temperature,
+                         const long long* request, const int* step, unsigned long long seed, int* out,
+                         cudaStream_t stream) {
+    if (n == 0) return 0;
+    FD_REQUIRE(V > 0, -2, "sample: vocabulary %d", V);
+    FD_REQUIRE(temperature == nullptr || (request != nullptr && step != nullptr), -2,
+               "sample: temperature sampling needs request ids and step counters");
+    sample_kernel<<<n, 512, 0, stream>>>(logits, V, temperature, request, step, seed, out);
+    return check_launch("sample");
+}

@@ -1,0 +1,223 @@
+"""Python side of the CUDA kernel library: one thin function per launcher.
+
+The role of ``engine/ops_cuda.py`` + ``kernels/bindings.cpp`` in
+davidjoyme/flashdecode-cuda (bindings.cpp:24-63,79-164), without an op
+registry or an alternative backend: these functions are the only
+implementation, they check what the kernels assume (device, dtype,
+contiguity) and raise with the kernel library's own message when a launcher
+refuses a size.  There is no CPU path; importing this module on a machine
+without the built library builds it, and calling any function without a CUDA
+device fails.
+
+Tensors are passed as raw pointers on torch's current stream, so launches are
+ordered with torch's own work and can be captured into a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+STATUS_BAD_TOKEN = 1
+STATUS_BAD_BLOCK = 2
+STATUS_BAD_POSITION = 4
+STATUS_WAIT_TIMEOUT = 8
+_STATUS_TEXT = {
+    STATUS_BAD_TOKEN: "a token id lies outside the embedding table",
+    STATUS_BAD_BLOCK: "a cached token maps to no allocated block",
+    STATUS_BAD_POSITION: "a position lies beyond the rotation table",
+    STATUS_WAIT_TIMEOUT: "a bounded wait inside a kernel ran out",
+}
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or a launch failed."""
+
+
+def _dt(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return 0
+    if t == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {t}")
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded kernel library; built on first use if it is missing or stale."""
+    global _lib
+    if _lib is None:
+        path = _build.build()
+        try:
+            _lib = ctypes.CDLL(str(path))
+        except OSError as e:  # pragma: no cover - environment failure
+            raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from e
+        _declare(_lib)
+    return _lib
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+    L.fd_last_error.restype = ctypes.c_char_p
+    L.fd_last_error.argtypes = []
+    sigs = {
+        "fd_device_arch": [],
+        "fd_sm_count": [],
+        "fd_embed": [P, P, I, P, I, I, I, P, P],
+        "fd_add_rmsnorm": [P, I, I, LL, P, I, P, I, F, P, I, P, I, I, P],
+        "fd_silu_mul": [P, P, I, I, I, P],
+        "fd_rope_append": [P, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P],
+        "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
+        "fd_attn_simt_qt": [I],
+        "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
+        "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P],
+    }
+    for name, args in sigs.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = I
+    L.fd_attn_scratch_floats.argtypes = [I, I, I, I]
+    L.fd_attn_scratch_floats.restype = LL
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib().fd_last_error().decode())
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernels take CUDA tensors only; there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError("kernels take contiguous tensors")
+    return t.data_ptr()
+
+
+def require_device() -> None:
+    """Fail loudly unless a CUDA device of compute capability 10.x is current."""
+    if not torch.cuda.is_available():
+        raise KernelError("flashdecode_cuda_b200 needs a CUDA device (B200, sm_100a); none is available "
+                          "and there is no CPU fallback")
+    arch = lib().fd_device_arch()
+    if arch < 0:
+        _check(arch)
+    if arch // 10 != 10:
+        raise KernelError(f"the kernels are built for sm_100a only; this device is sm_{arch}")
+
+
+def sm_count() -> int:
+    return lib().fd_sm_count()
+
+
+def status_message(word: int) -> str:
+    return "; ".join(text for bit, text in _STATUS_TEXT.items() if word & bit) or "ok"
+
+
+# ---------------------------------------------------------------------------
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, resid: torch.Tensor, status: torch.Tensor) -> None:
+    """resid[t] = float(table[tokens[t]]); tokens int32 [T], resid float32 [T, H]."""
+    T = tokens.numel()
+    V, H = table.shape
+    assert tokens.dtype == torch.int32 and resid.dtype == torch.float32 and resid.shape[-1] == H
+    _check(lib().fd_embed(_ptr(tokens), _ptr(table), _dt(table.dtype), _ptr(resid), T, H, V,
+                          _ptr(status), _stream()))
+
+
+def add_rmsnorm(delta: Optional[torch.Tensor], resid: torch.Tensor, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, n_out: Optional[int] = None,
+                write_resid: bool = True, n_parts: int = 1) -> None:
+    """out[j] = rmsnorm(resid[r] + delta[r]) * weight with r = rows[j] (or j);
+    resid[r] takes the sum when ``write_resid``.  ``delta`` None: plain norm.
+    ``delta`` with ``n_parts`` > 1 is [n_parts, rows, H], summed in order."""
+    H = resid.shape[-1]
+    if n_out is None:
+        n_out = rows.numel() if rows is not None else resid.numel() // H
+    assert resid.dtype == torch.float32 and out.shape[-1] == H and weight.numel() == H
+    part_stride = 0
+    if delta is not None and n_parts > 1:
+        part_stride = delta.numel() // n_parts
+    _check(lib().fd_add_rmsnorm(_ptr(delta), _dt(delta.dtype) if delta is not None else _dt(out.dtype),
+                                n_parts, part_stride, _ptr(resid), int(write_resid), _ptr(weight),
+                                _dt(weight.dtype), float(eps), _ptr(out), _dt(out.dtype), _ptr(rows),
+                                n_out, H, _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]."""
+    M, I2 = gate_up.shape
+    assert out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
+    _check(lib().fd_silu_mul(_ptr(gate_up), _ptr(out), _dt(out.dtype), M, I2 // 2, _stream()))
+
+
+def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                tok_row: torch.Tensor, tok_pos: torch.Tensor, row_slot: torch.Tensor,
+                k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor) -> None:
+    """Rotate q and k of every token at its position; append k and v to the
+    paged pools [num_blocks, n_kv, block_size, d] (unless ``write_kv`` is off)."""
+    T = qkv.shape[0]
+    assert qkv.shape[1] == (n_q + 2 * n_kv) * head_dim and q_out.shape == (T, n_q * head_dim)
+    assert cos.dtype == torch.float32 and cos.shape[1] == head_dim // 2
+    assert k_pool.dtype == qkv.dtype and q_out.dtype == qkv.dtype
+    num_blocks, _, block_size, _ = k_pool.shape
+    _check(lib().fd_rope_append(_ptr(qkv), _ptr(q_out), _dt(qkv.dtype), _ptr(cos), _ptr(sin), cos.shape[0],
+                                _ptr(tok_row), _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool),
+                                _ptr(block_table), block_table.shape[1], num_blocks, block_size, T, n_q, n_kv,
+                                head_dim, int(write_kv), _ptr(status), _stream()))
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] w[N, K]^T + bias on the CUDA cores (fixed k order)."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and w.dtype == x.dtype
+    _check(lib().fd_gemm_simt(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _dt(x.dtype),
+                              _dt(bias.dtype) if bias is not None else 0, _dt(out.dtype), M, N, K, _stream()))
+
+
+def attention_scratch_floats(n_tokens: int, n_q: int, head_dim: int, n_splits: int) -> int:
+    return int(lib().fd_attn_scratch_floats(n_tokens, n_q, head_dim, n_splits))
+
+
+def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                   block_table: torch.Tensor, tok_row: torch.Tensor, row_slot: torch.Tensor,
+                   row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
+                   n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
+                   window: int = 0, n_splits: int = 1, split_len: int = 0,
+                   scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """Causal GQA attention of the step's tokens over the paged cache."""
+    T = q.shape[0]
+    num_blocks, _, block_size, _ = k_pool.shape
+    assert q.dtype == k_pool.dtype == out.dtype
+    if n_splits > 1:
+        assert scratch is not None and scratch.dtype == torch.float32
+        assert scratch.numel() >= attention_scratch_floats(T, n_q, head_dim, n_splits)
+    _check(lib().fd_attention_simt(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype),
+                                   _ptr(block_table), block_table.shape[1], num_blocks, block_size,
+                                   _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len),
+                                   _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale),
+                                   int(window), n_splits, split_len, _ptr(scratch), _ptr(status), _stream()))
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+           request: Optional[torch.Tensor] = None, step: Optional[torch.Tensor] = None, seed: int = 0) -> None:
+    """out[i] = argmax (greedy) or a Gumbel-max draw from softmax(logits[i] / T_i)."""
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32
+    if temperature is not None:
+        assert temperature.dtype == torch.float32 and request.dtype == torch.int64 and step.dtype == torch.int32
+    _check(lib().fd_sample(_ptr(logits), n, V, _ptr(temperature), _ptr(request), _ptr(step),
+                           seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _stream()))

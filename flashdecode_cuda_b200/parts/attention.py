@@ -1,0 +1,107 @@
+"""Grouped-query attention over the paged cache: the mixer of this architecture."""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_part
+from ..weights.spec import TensorSpec
+from .base import KVRequest, LayerCache, Mixer, Runtime
+from .linear import matmul
+
+
+def plan_splits(n_rows: int, n_kv: int, kv_len_bound: int, sm_count: int):
+    """How a decode step cuts each sequence's keys: (n_splits, split_len).
+    Enough CTAs for about two per SM; split boundaries are multiples of
+    ``split_len`` in absolute position, so they do not move with the batch's
+    contents (only with its size and the length bound)."""
+    ctas = max(1, n_rows * n_kv)
+    want = max(1, (2 * sm_count) // ctas)
+    split_len = -(-kv_len_bound // want)
+    split_len = max(64, -(-split_len // 32) * 32)
+    n_splits = max(1, -(-kv_len_bound // split_len))
+    return n_splits, split_len
+
+
+@register_part("mixer", "gqa_attention")
+class GQAAttention(Mixer):
+    """q/k/v projections (bias optional), rotary encoding of q and k fused with
+    the append to the cache, causal attention of each new token over its
+    sequence's cached keys, output projection.
+
+    Formulas: engine/model.py:188-208,273-293 and engine/ops.py:153-194 of
+    davidjoyme/flashdecode-cuda; query head h reads KV head h // G; scale
+    1/sqrt(head_dim).  ``window``: a query sees only the last ``window`` keys.
+    ``bias``: True = required, False = refused, None = taken if the checkpoint
+    has it (the reference's rule, engine/loader.py:29-33).
+    """
+
+    def __init__(self, prefix: str, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 position: "RotaryHalf", window: Optional[int] = None, bias: Optional[bool] = None):
+        self.prefix = prefix
+        self.hidden_size, self.n_q, self.n_kv, self.d = hidden_size, n_heads, n_kv_heads, head_dim
+        self.position, self.window, self.bias = position, window, bias
+        self.scale = 1.0 / math.sqrt(head_dim)
+
+    # --- what it needs -------------------------------------------------
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H, d = self.prefix, self.hidden_size, self.d
+        specs = [TensorSpec(f"{p}.q_proj.weight", (self.n_q * d, H)),
+                 TensorSpec(f"{p}.k_proj.weight", (self.n_kv * d, H)),
+                 TensorSpec(f"{p}.v_proj.weight", (self.n_kv * d, H)),
+                 TensorSpec(f"{p}.o_proj.weight", (H, self.n_q * d))]
+        if self.bias is not False:
+            opt = self.bias is None
+            specs += [TensorSpec(f"{p}.q_proj.bias", (self.n_q * d,), "vector", optional=opt, init="bias"),
+                      TensorSpec(f"{p}.k_proj.bias", (self.n_kv * d,), "vector", optional=opt, init="bias"),
+                      TensorSpec(f"{p}.v_proj.bias", (self.n_kv * d,), "vector", optional=opt, init="bias")]
+        return specs
+
+    def kv_request(self) -> KVRequest:
+        return KVRequest(self.n_kv, self.d, self.window)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        names = [f"{p}.{x}_proj" for x in "qkv"]
+        # one [ (n_q + 2 n_kv) d, H ] matrix: one product instead of three
+        self.w_qkv = torch.cat([tensors.pop(f"{n}.weight") for n in names], dim=0).contiguous()
+        have = [f"{n}.bias" in tensors for n in names]
+        if any(have) and not all(have):
+            raise ValueError(f"{p}: q/k/v biases must be all present or all absent")
+        self.b_qkv = torch.cat([tensors.pop(f"{n}.bias") for n in names]).contiguous() if all(have) else None
+        self.w_o = tensors[f"{p}.o_proj.weight"]
+
+    def weight_bytes(self) -> int:
+        n = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
+        if self.b_qkv is not None:
+            n += self.b_qkv.numel() * self.b_qkv.element_size()
+        return n
+
+    # --- a step ----------------------------------------------------------
+    def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
+        T, d = ctx.T, self.d
+        ws = ctx.ws
+        qkv = ws.get("qkv", (T, (self.n_q + 2 * self.n_kv) * d), x.dtype)
+        matmul(x, self.w_qkv, self.b_qkv, qkv)
+        q = ws.get("q_rot", (T, self.n_q * d), x.dtype)
+        K.rope_append(qkv, q, self.position.cos, self.position.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
+                      lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status)
+        attn = ws.get("attn", (T, self.n_q * d), x.dtype)
+        n_splits, split_len, scratch = 1, 0, None
+        if ctx.max_q_len == 1:
+            n_splits, split_len = plan_splits(ctx.n_rows, self.n_kv, ctx.kv_len_bound, self.rt.sm_count)
+            if n_splits > 1:
+                scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, self.n_q, d, n_splits),),
+                                 torch.float32)
+        K.attention_simt(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot,
+                         ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len,
+                         self.n_q, self.n_kv, d, self.scale, self.window or 0, n_splits, split_len, scratch,
+                         self.rt.status)
+        out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
+        matmul(attn, self.w_o, None, out)
+        return out

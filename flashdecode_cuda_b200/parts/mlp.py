@@ -1,0 +1,49 @@
+"""Dense gated feed-forward (SwiGLU)."""
+
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels as K
+from ..registry import register_part
+from ..weights.spec import TensorSpec
+from .base import FeedForward, Runtime
+from .linear import matmul
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    """down( silu(gate(x)) * up(x) ), no biases (engine/model.py:213-216 and
+    engine/ops.py:201-204 of davidjoyme/flashdecode-cuda).  gate and up are one
+    [2I, H] matrix here, so they are one product."""
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int):
+        self.prefix, self.hidden_size, self.inter = prefix, hidden_size, intermediate_size
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        p, H, I = self.prefix, self.hidden_size, self.inter
+        return [TensorSpec(f"{p}.gate_proj.weight", (I, H)),
+                TensorSpec(f"{p}.up_proj.weight", (I, H)),
+                TensorSpec(f"{p}.down_proj.weight", (H, I))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        p = self.prefix
+        self.w_gate_up = torch.cat([tensors.pop(f"{p}.gate_proj.weight"),
+                                    tensors.pop(f"{p}.up_proj.weight")], dim=0).contiguous()
+        self.w_down = tensors[f"{p}.down_proj.weight"]
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        T, ws = ctx.T, ctx.ws
+        gu = ws.get("gate_up", (T, 2 * self.inter), x.dtype)
+        matmul(x, self.w_gate_up, None, gu)
+        act = ws.get("ffn_act", (T, self.inter), x.dtype)
+        K.silu_mul(gu, act)
+        out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
+        matmul(act, self.w_down, None, out)
+        return out

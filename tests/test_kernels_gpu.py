@@ -1,0 +1,361 @@
+"""Each CUDA kernel alone against a plain PyTorch float32/float64 reference of
+the same operation, at sizes other than the engine's tiny models: head sizes
+in steps of 16, groups that are no power of two, widths and vocabularies that
+are no multiple of anything useful."""
+
+import math
+
+import pytest
+import torch
+
+from flashdecode_cuda_b200 import kernels as K
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 1e-5, "bfloat16": 1.2e-2}
+
+
+def rel(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).abs().max()) / max(float(want.abs().max()), 1e-9)
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("V,H,T", [(100, 48, 7), (333, 1536, 33), (50, 5, 3)])
+def test_embed(dtype, V, H, T):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, H, generator=g).to(DT[dtype]).to(DEV)
+    tokens = torch.randint(0, V, (T,), generator=g, dtype=torch.int32).to(DEV)
+    resid = torch.full((T, H), 7.0, device=DEV)
+    st = status()
+    K.embed(tokens, table, resid, st)
+    assert torch.equal(resid, table[tokens.long()].float())
+    assert int(st.item()) == 0
+    # an id outside the table is skipped and reported, not read
+    bad = tokens.clone()
+    bad[T // 2] = V + 5
+    K.embed(bad, table, resid, st)
+    assert int(st.item()) == K.STATUS_BAD_TOKEN
+    assert float(resid[T // 2].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows,H", [(5, 80), (3, 1537), (64, 4096), (2, 9)])
+def test_add_rmsnorm(dtype, rows, H):
+    g = torch.Generator().manual_seed(1)
+    dt = DT[dtype]
+    delta = torch.randn(rows, H, generator=g).to(dt).to(DEV)
+    resid = torch.randn(rows, H, generator=g).to(DEV)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(dt).to(DEV)
+    eps = 3e-6
+    out = torch.empty(rows, H, dtype=dt, device=DEV)
+    r2 = resid.clone()
+    K.add_rmsnorm(delta, r2, w, eps, out)
+    x = resid.double() + delta.double()
+    assert rel(r2, x) < 1e-6
+    want = P.rmsnorm(x, w.double(), eps)
+    assert rel(out, want) < (1e-5 if dtype == "float32" else 6e-3)
+    # plain norm (no delta), only chosen rows, residual untouched
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=dt, device=DEV)
+    r3 = resid.clone()
+    K.add_rmsnorm(None, r3, w, eps, out2, rows=idx)
+    assert torch.equal(r3, resid)
+    assert rel(out2, P.rmsnorm(resid.double()[idx.long()], w.double(), eps)) < (1e-5 if dtype == "float32" else 6e-3)
+    # chosen rows with a delta that is not written back
+    K.add_rmsnorm(delta, r3, w, eps, out2, rows=idx, write_resid=False)
+    assert torch.equal(r3, resid)
+    assert rel(out2, want[idx.long()]) < (1e-5 if dtype == "float32" else 6e-3)
+    # a 32-bit weight vector with 16-bit activations
+    if dtype == "bfloat16":
+        K.add_rmsnorm(delta, resid.clone(), w.float(), eps, out)
+        assert rel(out, want) < 6e-3
+
+
+def test_add_rmsnorm_partial_sums():
+    g = torch.Generator().manual_seed(2)
+    parts = torch.randn(3, 6, 200, generator=g).to(DEV)
+    resid = torch.randn(6, 200, generator=g).to(DEV)
+    w = torch.ones(200, device=DEV)
+    out = torch.empty(6, 200, device=DEV)
+    r = resid.clone()
+    K.add_rmsnorm(parts, r, w, 1e-6, out, n_parts=3, n_out=6)
+    x = resid.double() + parts.double().sum(0)
+    assert rel(r, x) < 1e-6
+    assert rel(out, P.rmsnorm(x, w.double(), 1e-6)) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,I", [(3, 176), (65, 8960), (1, 7)])
+def test_silu_mul(dtype, M, I):
+    g = torch.Generator().manual_seed(3)
+    gu = (2 * torch.randn(M, 2 * I, generator=g)).to(DT[dtype]).to(DEV)
+    out = torch.empty(M, I, dtype=DT[dtype], device=DEV)
+    K.silu_mul(gu, out)
+    want = P.swiglu(gu[:, :I].double(), gu[:, I:].double())
+    assert rel(out, want) < (1e-6 if dtype == "float32" else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (33, 100, 48), (70, 333, 1537), (8, 2048, 1536), (130, 64, 66)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_simt(dtype, M, N, K_, bias):
+    g = torch.Generator().manual_seed(4)
+    dt = DT[dtype]
+    x = torch.randn(M, K_, generator=g).to(dt).to(DEV)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(dt).to(DEV)
+    b = torch.randn(N, generator=g).to(dt).to(DEV) if bias else None
+    out = torch.empty(M, N, dtype=dt, device=DEV)
+    K.gemm_simt(x, w, b, out)
+    want = P.linear(x.double(), w.double(), b.double() if bias else None)
+    assert rel(out, want) < (2e-6 if dtype == "float32" else 5e-3)
+    if dtype == "bfloat16":                      # float32 output from 16-bit operands (logits)
+        out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        K.gemm_simt(x, w, b, out32)
+        assert rel(out32, want) < 2e-6
+
+
+def test_gemm_simt_rows_do_not_depend_on_the_batch():
+    """The same row gives the same bits alone and among 100 others."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(101, 300, generator=g).to(DEV)
+    w = torch.randn(77, 300, generator=g).to(DEV)
+    big = torch.empty(101, 77, device=DEV)
+    one = torch.empty(1, 77, device=DEV)
+    K.gemm_simt(x, w, None, big)
+    K.gemm_simt(x[70:71].contiguous(), w, None, one)
+    assert torch.equal(big[70:71], one)
+
+
+# ---------------------------------------------------------------------------
+# paged cache helpers for the rope and attention kernels
+# ---------------------------------------------------------------------------
+
+def scrambled_table(lens, block_size, n_slots, gen, spare=3):
+    """Block table [n_slots, max_blocks] whose blocks are handed out in a
+    random order, so a kernel that ignores the table cannot pass."""
+    per = [-(-n // block_size) for n in lens]
+    total = sum(per) + spare
+    perm = torch.randperm(total, generator=gen).tolist()
+    width = max(per) + 1
+    table = torch.full((n_slots, width), -1, dtype=torch.int32)
+    it = iter(perm)
+    slots = torch.randperm(n_slots, generator=gen)[:len(lens)].tolist()
+    for s, nb in zip(slots, per):
+        for c in range(nb):
+            table[s, c] = next(it)
+    return table, slots, total
+
+
+def fill_pools(k_seqs, v_seqs, table, slots, block_size, total_blocks, dtype, poison=None):
+    """Pools [blocks, n_kv, block_size, d] holding the given per-sequence keys
+    and values; untouched places hold ``poison`` (NaN by default: nothing may
+    read beyond a sequence's length)."""
+    n_kv, d = k_seqs[0].shape[1:]
+    fill = float("nan") if poison is None else poison
+    kp = torch.full((total_blocks, n_kv, block_size, d), fill, dtype=dtype)
+    vp = torch.full_like(kp, fill)
+    for ks, vs, s in zip(k_seqs, v_seqs, slots):
+        for pos in range(ks.shape[0]):
+            b = int(table[s, pos // block_size])
+            kp[b, :, pos % block_size] = ks[pos].to(dtype)
+            vp[b, :, pos % block_size] = vs[pos].to(dtype)
+    return kp.to(DEV), vp.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_q,n_kv,d,bs", [(6, 2, 48, 4), (5, 5, 16, 16), (12, 2, 128, 16), (7, 1, 80, 32)])
+def test_rope_append(dtype, n_q, n_kv, d, bs):
+    g = torch.Generator().manual_seed(6)
+    dt = DT[dtype]
+    ctx = [3, 0, 37]                 # cached before the step
+    new = [5, 9, 1]                  # new tokens of each row
+    lens = [c + n for c, n in zip(ctx, new)]
+    table, slots, total = scrambled_table(lens, bs, 5, g)
+    T = sum(new)
+    qkv = torch.randn(T, (n_q + 2 * n_kv) * d, generator=g).to(dt)
+    theta = 12345.0
+    n_pos = 64
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2).float() / d))
+    fr = torch.outer(torch.arange(n_pos).float(), inv)
+    cos, sin = fr.cos().to(DEV), fr.sin().to(DEV)
+    tok_row = torch.tensor([r for r, n in enumerate(new) for _ in range(n)], dtype=torch.int32)
+    tok_pos = torch.tensor([c + i for c, n in zip(ctx, new) for i in range(n)], dtype=torch.int32)
+    kp = torch.zeros(total, n_kv, bs, d, dtype=dt, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.empty(T, n_q * d, dtype=dt, device=DEV)
+    st = status()
+    K.rope_append(qkv.to(DEV), q_out, cos, sin, tok_row.to(DEV), tok_pos.to(DEV),
+                  torch.tensor(slots, dtype=torch.int32, device=DEV), kp, vp, table.to(DEV),
+                  n_q, n_kv, d, True, st)
+    assert int(st.item()) == 0
+    x = qkv.double().view(T, n_q + 2 * n_kv, d)
+    c2, s2 = P.rope_tables(d, n_pos, theta)
+    rot = P.apply_rope(x[:, :n_q + n_kv], c2[tok_pos.long()], s2[tok_pos.long()])
+    tol = 1e-6 if dtype == "float32" else 5e-3
+    assert rel(q_out.view(T, n_q, d), rot[:, :n_q]) < tol
+    for t in range(T):
+        s, pos = slots[int(tok_row[t])], int(tok_pos[t])
+        b = int(table[s, pos // bs])
+        assert rel(kp[b, :, pos % bs], rot[t, n_q:]) < tol
+        assert torch.equal(vp[b, :, pos % bs].cpu(), qkv.view(T, n_q + 2 * n_kv, d)[t, n_q + n_kv:])
+    # nothing else in the pools was touched
+    written = sum(new) * n_kv * d
+    assert int((kp != 0).sum().item()) <= written
+    # a padding row (slot -1) writes nothing and reports nothing
+    kp.zero_()
+    K.rope_append(qkv.to(DEV), q_out, cos, sin, tok_row.to(DEV), tok_pos.to(DEV),
+                  torch.tensor([-1, -1, -1], dtype=torch.int32, device=DEV), kp, vp, table.to(DEV),
+                  n_q, n_kv, d, True, st)
+    assert int(st.item()) == 0 and float(kp.abs().max()) == 0.0
+
+
+def attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window):
+    """Plain causal GQA attention of the new tokens of every row (float64)."""
+    G = n_q // n_kv
+    outs = []
+    o = 0
+    for ks, vs, c, n in zip(k_seqs, v_seqs, ctx, new):
+        qq = q[o:o + n].double().view(n, n_q, d)
+        o += n
+        out = torch.zeros(n, n_q, d, dtype=torch.float64)
+        for i in range(n):
+            pos = c + i
+            lo = max(0, pos - window + 1) if window else 0
+            for h in range(n_q):
+                sc = (ks[lo:pos + 1, h // G].double() @ qq[i, h]) * scale
+                out[i, h] = torch.softmax(sc, 0) @ vs[lo:pos + 1, h // G].double()
+        outs.append(out.view(n, n_q * d))
+    return torch.cat(outs)
+
+
+def run_attention(dtype, n_q, n_kv, d, bs, ctx, new, window=0, n_splits=1, split_len=0, seed=7,
+                  spike=None, pad_rows=0):
+    g = torch.Generator().manual_seed(seed)
+    dt = DT[dtype]
+    lens = [c + n for c, n in zip(ctx, new)]
+    table, slots, total = scrambled_table(lens, bs, len(lens) + 2, g)
+    k_seqs = [torch.randn(n, n_kv, d, generator=g).to(dt) for n in lens]
+    v_seqs = [torch.randn(n, n_kv, d, generator=g).to(dt) for n in lens]
+    T = sum(new)
+    q = torch.randn(T, n_q * d, generator=g).to(dt)
+    if spike is not None:
+        # one far key and one query made to match: its score stands out, so a
+        # kernel that drops that key (a split boundary, a window edge) shows
+        row, key_pos = spike
+        k_seqs[row][key_pos] *= 6.0
+        q.view(T, n_q, d)[sum(new[:row + 1]) - 1] = k_seqs[row][key_pos].repeat_interleave(n_q // n_kv, 0) * 0.8
+    kp, vp = fill_pools(k_seqs, v_seqs, table, slots, bs, total, dt)
+    rows = len(new) + pad_rows
+    new_p, ctx_p, slots_p = new + [1] * pad_rows, ctx + [0] * pad_rows, slots + [-1] * pad_rows
+    Tp = T + pad_rows
+    qp = torch.cat([q, torch.zeros(pad_rows, n_q * d, dtype=dt)]).to(DEV)
+    starts = [sum(new_p[:i]) for i in range(rows)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tok_row = i32([r for r, n in enumerate(new_p) for _ in range(n)])
+    out = torch.full((Tp, n_q * d), float("nan"), dtype=dt, device=DEV)
+    scratch = None
+    if n_splits > 1:
+        scratch = torch.full((K.attention_scratch_floats(Tp, n_q, d, n_splits),), float("nan"), device=DEV)
+    st = status()
+    scale = 1.0 / math.sqrt(d)
+    K.attention_simt(qp, kp, vp, out, table.to(DEV), tok_row, i32(slots_p), i32(starts), i32(new_p), i32(ctx_p),
+                     rows, max(new_p), n_q, n_kv, d, scale, window, n_splits, split_len, scratch, st)
+    assert int(st.item()) == 0
+    want = attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window)
+    return out[:T], want, out[T:]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_q,n_kv,d,bs", [(6, 2, 48, 4), (5, 1, 16, 16), (12, 2, 128, 16), (7, 7, 80, 32),
+                                           (4, 2, 256, 8), (28, 4, 128, 16)])
+def test_attention_prompts(dtype, n_q, n_kv, d, bs):
+    """Whole prompts of unequal lengths, some continuing a cached prefix."""
+    got, want, _ = run_attention(dtype, n_q, n_kv, d, bs, ctx=[0, 0, 13, 0], new=[1, 37, 22, 70])
+    assert rel(got, want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 5, 32, 33])
+def test_attention_window(dtype, window):
+    got, want, _ = run_attention(dtype, 6, 2, 32, 8, ctx=[0, 40, 7], new=[50, 9, 1], window=window)
+    assert rel(got, want) < TOL[dtype]
+    got, want, _ = run_attention(dtype, 6, 2, 32, 8, ctx=[64, 40, 7], new=[1, 1, 1], window=window,
+                                 n_splits=3, split_len=32)
+    assert rel(got, want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_splits,split_len", [(1, 0), (2, 160), (4, 96), (9, 32), (16, 64)])
+def test_attention_decode_splits(dtype, n_splits, split_len):
+    """One new token per row over cached lengths 0..300; more splits than some
+    rows have keys for (empty partial results), and a padding row."""
+    got, want, pad = run_attention(dtype, 12, 2, 64, 16, ctx=[0, 15, 16, 299, 100], new=[1] * 5,
+                                   n_splits=n_splits, split_len=split_len, pad_rows=2)
+    assert rel(got, want) < TOL[dtype]
+    if n_splits > 1:
+        assert float(pad.float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_far_key_stands_out(dtype):
+    """Among 700 keys one early key carries nearly all the weight of the last
+    query; it lies in the first split and in a block far from the others."""
+    for key_pos in (0, 31, 32, 255, 256, 698):
+        got, want, _ = run_attention(dtype, 6, 2, 64, 16, ctx=[699, 40], new=[1, 1], n_splits=6, split_len=128,
+                                     spike=(0, key_pos))
+        assert rel(got, want) < TOL[dtype], key_pos
+        got, want, _ = run_attention(dtype, 6, 2, 64, 16, ctx=[0, 0], new=[700, 3], spike=(0, key_pos))
+        assert rel(got, want) < TOL[dtype], key_pos
+
+
+def test_attention_refuses_what_it_cannot_do():
+    with pytest.raises(K.KernelError, match="head size"):
+        run_attention("float32", 4, 2, 24, 4, ctx=[0], new=[3])
+    with pytest.raises(K.KernelError, match="multiple"):
+        run_attention("float32", 5, 2, 32, 4, ctx=[0], new=[3])
+
+
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("V", [7, 256, 333, 151936])
+def test_sample_greedy_and_temperature(V):
+    g = torch.Generator().manual_seed(9)
+    n = 5
+    logits = torch.randn(n, V, generator=g)
+    logits[1, V // 2] = logits[1].max() + 1          # a clear winner
+    logits[2, :] = 0.25                              # all tied: the lowest index wins
+    logits[3, V - 1] = logits[3, 0] = 9.0            # two tied winners
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    K.sample(logits.to(DEV), out)
+    want = [P.sample(logits[i], 0.0, 0, 0, 0) for i in range(n)]
+    assert out.tolist() == want
+    assert out[2].item() == 0 and out[3].item() == 0 and out[1].item() == V // 2
+    if V > 1000:
+        n = 2
+    temps = [0.8, 0.0, 1.3, 0.5, 2.0][:n]
+    reqs = [3, 1, 2 ** 40 + 5, 0, 7][:n]
+    steps = [0, 5, 1, 2, 9][:n]
+    K.sample(logits[:n].to(DEV), out[:n], torch.tensor(temps, device=DEV),
+             torch.tensor(reqs, dtype=torch.int64, device=DEV), torch.tensor(steps, dtype=torch.int32, device=DEV),
+             seed=2 ** 33 + 17)
+    want = [P.sample(logits[i], temps[i], 2 ** 33 + 17, reqs[i], steps[i]) for i in range(n)]
+    assert out[:n].tolist() == want
+
+
+def test_sample_temperature_follows_the_distribution():
+    """Over many (request, step) keys the draws follow softmax(logits / T)."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]])
+    n = 4000
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    K.sample(logits.expand(n, 5).contiguous().to(DEV), out, torch.full((n,), 0.7, device=DEV),
+             torch.arange(n, dtype=torch.int64, device=DEV), torch.zeros(n, dtype=torch.int32, device=DEV), seed=1)
+    freq = torch.bincount(out.cpu().long(), minlength=5).double() / n
+    want = torch.softmax(logits[0].double() / 0.7, 0)
+    assert float((freq - want).abs().max()) < 0.03
