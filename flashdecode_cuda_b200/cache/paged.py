@@ -78,7 +78,7 @@ class KVGroup:
         self.alloc = IdAllocator(num_blocks, "block")
         self.table_host = np.full((max_slots, max_blocks_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, max_blocks_per_seq), -1, dtype=torch.int32, device=device)
-        self._pending: List[Tuple[int, int, int]] = []     # (slot, column, block) not yet on the device
+        self._pending: Dict[Tuple[int, int], int] = {}     # (slot, column) -> block, not yet on the device
 
     def k_pool(self, layer: int) -> torch.Tensor:
         return self.pool[layer, 0]
@@ -88,15 +88,15 @@ class KVGroup:
 
     def set_entry(self, slot: int, col: int, block: int) -> None:
         self.table_host[slot, col] = block
-        self._pending.append((slot, col, block))
+        self._pending[(slot, col)] = block       # a later value for the same entry replaces the earlier
 
     def sync(self) -> None:
         """Bring the device table up to date with one small copy."""
         if not self._pending:
             return
         width = self.max_blocks_per_seq
-        idx = torch.tensor([s * width + c for s, c, _ in self._pending], dtype=torch.int64)
-        val = torch.tensor([b for _, _, b in self._pending], dtype=torch.int32)
+        idx = torch.tensor([s * width + c for s, c in self._pending], dtype=torch.int64)
+        val = torch.tensor(list(self._pending.values()), dtype=torch.int32)
         self._pending.clear()
         dev = self.table.device
         if dev.type == "cuda":

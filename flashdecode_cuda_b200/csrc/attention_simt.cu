@@ -320,7 +320,7 @@ typedef __nv_bfloat16 bf16;
 // Largest number of query tokens a CTA takes for a group size (0: unsupported).
 extern "C" int fd_attn_simt_qt(int G) { return G >= 1 && G <= RMAX ? (RMAX / G > 16 ? 16 : RMAX / G) : 0; }
 
-// Floats of scratch the split form needs: part_m, part_l [T, n_q, n_splits] and part_acc [.., d].
+// Floats of scratch the split form needs: part_acc [T, n_q, n_splits, d], then part_m and part_l [T, n_q, n_splits].
 extern "C" long long fd_attn_scratch_floats(int T, int n_q, int d, int n_splits) {
     return (long long)T * n_q * n_splits * (d + 2);
 }
@@ -345,13 +345,18 @@ extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* 
     FD_REQUIRE(n_splits == 1 || (split_len > 0 && split_len % KT == 0), -2,
                "attention: split length %d must be a positive multiple of %d", split_len, KT);
     FD_REQUIRE(n_splits == 1 || scratch != nullptr, -2, "attention: split form needs scratch memory");
+    FD_REQUIRE((uintptr_t)scratch % 16 == 0 && (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0, -2,
+               "attention: the cache pools and the scratch memory must be 16-byte aligned");
+    FD_REQUIRE(n_splits == 1 || T <= 65535, -2, "attention: the split form takes at most 65535 tokens, got %d", T);
     FD_REQUIRE(n_rows <= 65535 && n_kv <= 65535, -2, "attention: batch of %d rows too large", n_rows);
 
     AttnParams p;
     p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.out = out;
     const size_t n_part = (size_t)T * n_q * n_splits;
-    p.part_m = scratch; p.part_l = scratch ? scratch + n_part : nullptr;
-    p.part_acc = scratch ? scratch + 2 * n_part : nullptr;
+    // accumulators first: they are stored as float4 and must stay 16-byte aligned
+    p.part_acc = scratch;
+    p.part_m = scratch ? scratch + n_part * d : nullptr;
+    p.part_l = scratch ? scratch + n_part * d + n_part : nullptr;
     p.block_table = block_table; p.row_slot = row_slot; p.row_q_start = row_q_start;
     p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len; p.status = status;
     p.max_blocks = max_blocks; p.num_blocks = num_blocks; p.block_size = block_size;

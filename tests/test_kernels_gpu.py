@@ -293,7 +293,7 @@ def test_attention_window(dtype, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("n_splits,split_len", [(1, 0), (2, 160), (4, 96), (9, 32), (16, 64)])
+@pytest.mark.parametrize("n_splits,split_len", [(1, 0), (2, 160), (4, 96), (10, 32), (16, 64)])
 def test_attention_decode_splits(dtype, n_splits, split_len):
     """One new token per row over cached lengths 0..300; more splits than some
     rows have keys for (empty partial results), and a padding row."""
@@ -302,6 +302,16 @@ def test_attention_decode_splits(dtype, n_splits, split_len):
     assert rel(got, want) < TOL[dtype]
     if n_splits > 1:
         assert float(pad.float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_decode_splits_odd_counts(dtype):
+    """One row, three heads, an odd number of splits: every sub-array of the
+    scratch memory starts at an odd multiple of something."""
+    for n_q, n_kv, n_splits, split_len in ((3, 1, 3, 64), (5, 5, 7, 32), (1, 1, 5, 32)):
+        got, want, _ = run_attention(dtype, n_q, n_kv, 32, 16, ctx=[150], new=[1], n_splits=n_splits,
+                                     split_len=split_len)
+        assert rel(got, want) < TOL[dtype]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -73,7 +73,7 @@ def test_unequal_batches_one_after_another(engines, folders, name, dtype):
     cache = eng.model.new_cache(max_tokens=64 * 6, block_size=8, max_slots=4)
     for batch_no, lengths in enumerate([[9, 30, 17, 44], [40, 3, 21], [5, 5, 62, 13]]):
         reqs = prompts_for(V, lengths, seed=10 + batch_no)
-        decode = [6, 14, 2, 9][:len(reqs)]               # tokens of each request fed one by one
+        decode = [min(k, len(p) - 1) for k, p in zip([6, 14, 2, 9], reqs)]   # tokens of each request fed one by one
         slots = [cache.admit() for _ in reqs]
         live = list(range(len(reqs)))
         heads = [len(p) - k for p, k in zip(reqs, decode)]
