@@ -22,6 +22,7 @@ from ..cache.paged import PagedCache
 from ..config import load_config
 from ..sampling.sampler import Sampler
 from ..weights import loader as W
+from .decode import GraphDecoder
 from .generate import Backend, GenerationLoop, Request, Result
 from .model import Model
 
@@ -47,6 +48,8 @@ class Engine(Backend):
         self.sampler = Sampler(model.device)
         self.cache: Optional[PagedCache] = None
         self.seed = 0
+        self.use_graphs = model.device.type == "cuda"     # decode steps replay captured CUDA graphs
+        self._graph_decoder: Optional[GraphDecoder] = None
 
     # -- caches -----------------------------------------------------------
     def new_paged_cache(self, batch_size: int, max_len: int, block_size: int = 16,
@@ -75,10 +78,19 @@ class Engine(Backend):
         self.cache.release(slot)
 
     def run(self, slots, tokens, requests, steps) -> List[int]:
-        logits = self.model.step(self.cache, slots, tokens, "last")
         temps = [r.temperature for r in requests]
-        toks = self.sampler.sample(logits, temps, [r.request_id for r in requests], steps, self.seed)
+        rids = [r.request_id for r in requests]
+        if self.use_graphs and all(len(t) == 1 for t in tokens):
+            toks = self._decoder().run(slots, [t[0] for t in tokens], temps, rids, steps, self.seed)
+            return toks[:len(slots)].tolist()
+        logits = self.model.step(self.cache, slots, tokens, "last")
+        toks = self.sampler.sample(logits, temps, rids, steps, self.seed)
         return toks.tolist()
+
+    def _decoder(self) -> GraphDecoder:
+        if self._graph_decoder is None or self._graph_decoder.cache is not self.cache:
+            self._graph_decoder = GraphDecoder(self.model, self.cache)
+        return self._graph_decoder
 
     # -- generation ---------------------------------------------------------
     def _requests(self, input_ids, max_new_tokens, temperature, stop_token_ids) -> List[Request]:

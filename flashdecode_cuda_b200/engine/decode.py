@@ -1,0 +1,138 @@
+"""Decode steps replayed from CUDA graphs.
+
+A decode step of this model is a few hundred small kernels; launched one by
+one from Python their launch cost exceeds their run time (the finding of
+davidjoyme/flashdecode-cuda, README.md:105-111: ~93 us per eager op call, "the
+levers are launch count and graph capture").  Here a whole step - embedding,
+every layer, final norm, output head and the sampler - is captured once per
+batch-size bucket and replayed; per step the host only reserves cache blocks,
+uploads one small index array and launches the graph.
+
+A graph is tied to fixed device buffers (its own workspace) and to grid sizes,
+so it is keyed by the padded batch size, a bound on the longest sequence (it
+sizes the split of the keys) and the sampler's constants.  Padding rows carry
+slot -1; every kernel skips them, so padding changes no result.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import kernels as K
+from ..cache.paged import PagedCache
+from .model import Model, StepContext, Workspace
+
+BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+KV_BOUND_STEP = 1024
+
+
+def bucket_of(n: int) -> int:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return -(-n // 64) * 64
+
+
+class _Graph:
+    def __init__(self, ws: Workspace):
+        self.ws = ws
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.ctx: Optional[StepContext] = None
+        self.sampled: Optional[torch.Tensor] = None
+        self.temp = self.req = self.step = None
+        self.launches = 0
+
+
+class GraphDecoder:
+    """One-token-per-sequence steps of ``model`` over ``cache`` with sampling,
+    through captured graphs.  ``run`` takes host tokens and returns the device
+    tensor of sampled tokens; ``run_device_fed`` feeds the previous step's
+    sampled tokens without leaving the device."""
+
+    def __init__(self, model: Model, cache: PagedCache):
+        self.model, self.cache = model, cache
+        self.graphs: Dict[Tuple, _Graph] = {}
+        self.last: Optional[_Graph] = None
+        self.last_n = 0
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------
+    def _key(self, n: int, longest: int, greedy: bool, seed: int) -> Tuple:
+        bound = min(-(-longest // KV_BOUND_STEP) * KV_BOUND_STEP, self.cache.max_len)
+        return (bucket_of(n), bound, greedy, seed if not greedy else 0)
+
+    def _prepare(self, g: _Graph, key: Tuple, slots: Sequence[int], tokens: Sequence[int]) -> StepContext:
+        B, bound = key[0], key[1]
+        return self.model.make_context(self.cache, slots, [[int(t)] for t in tokens], "all",
+                                       pad_rows=B - len(slots), kv_len_bound=bound, ws=g.ws)
+
+    def _body(self, g: _Graph, ctx: StepContext, key: Tuple) -> None:
+        logits = self.model.forward(ctx)
+        if key[2]:
+            K.sample(logits, g.sampled)
+        else:
+            K.sample(logits, g.sampled, g.temp, g.req, g.step, key[3])
+
+    def _graph_for(self, key: Tuple, slots, tokens) -> Tuple[_Graph, StepContext]:
+        g = self.graphs.get(key)
+        if g is not None:
+            return g, self._prepare(g, key, slots, tokens)
+        B = key[0]
+        dev = self.model.device
+        g = _Graph(Workspace(dev))
+        g.sampled = torch.zeros(B, dtype=torch.int32, device=dev)
+        g.temp = torch.zeros(B, dtype=torch.float32, device=dev)
+        g.req = torch.zeros(B, dtype=torch.int64, device=dev)
+        g.step = torch.zeros(B, dtype=torch.int32, device=dev)
+        ctx = self._prepare(g, key, slots, tokens)
+        # one eager run: it allocates the workspace and writes this step's keys
+        # and values; the captured replay below rewrites the same values
+        self._body(g, ctx, key)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = K.LAUNCHES
+        with torch.cuda.graph(graph):
+            self._body(g, ctx, key)
+        g.launches = K.LAUNCHES - before          # this library's kernels in one replay
+        g.graph, g.ctx = graph, ctx
+        self.graphs[key] = g
+        return g, ctx
+
+    # ------------------------------------------------------------------
+    def run(self, slots: Sequence[int], tokens: Optional[Sequence[int]], temperatures: Optional[Sequence[float]] = None,
+            request_ids: Optional[Sequence[int]] = None, steps: Optional[Sequence[int]] = None,
+            seed: int = 0) -> torch.Tensor:
+        """Feed one token to each slot, sample one next token each.  Returns an
+        int32 device tensor whose first ``len(slots)`` entries are the tokens
+        (valid until the next call).  ``tokens`` None: use the tokens sampled by
+        the previous call (same slots, in the same order)."""
+        cache, n = self.cache, len(slots)
+        greedy = temperatures is None or not any(t > 0.0 for t in temperatures)
+        cache.reserve([(s, 1) for s in slots])
+        cache.sync()
+        longest = max(cache.length(s) for s in slots) + 1
+        key = self._key(n, longest, greedy, seed)
+        device_fed = tokens is None
+        if device_fed:
+            if self.last is None or self.last_n != n:
+                raise ValueError("no previous step with the same slots to take tokens from")
+            prev = self.last.sampled[:n]
+            tokens = [0] * n
+        g, ctx = self._graph_for(key, slots, tokens)
+        if device_fed:
+            ctx.tokens[:n].copy_(prev)
+        if not greedy:
+            B = key[0]
+            pad = B - n
+            g.temp.copy_(torch.tensor(list(temperatures) + [0.0] * pad, dtype=torch.float32), non_blocking=False)
+            g.req.copy_(torch.tensor(list(request_ids) + [0] * pad, dtype=torch.int64))
+            g.step.copy_(torch.tensor(list(steps) + [0] * pad, dtype=torch.int32))
+        g.graph.replay()
+        for s in slots:
+            cache.advance(s, 1)
+        self.last, self.last_n = g, n
+        self.launches_per_step = g.launches
+        return g.sampled

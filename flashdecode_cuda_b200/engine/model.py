@@ -321,8 +321,9 @@ class Model:
         flat = np.fromiter((t for seq in tokens for t in seq), dtype=np.int64, count=sum(counts))
         if flat.size and (flat.min() < 0 or flat.max() >= self.vocab_size):
             raise ValueError(f"token ids must lie in [0, {self.vocab_size}); got {int(flat.min())}..{int(flat.max())}")
-        wanted = self._wanted(counts, want)
         T, N = int(flat.size) + pad_rows, n + pad_rows
+        # "all" on a padded batch includes the padding rows: the count of wanted rows is then fixed
+        wanted = list(range(T)) if (pad_rows and want == "all") else self._wanted(counts, want)
         counts_p = np.asarray(counts + [1] * pad_rows, dtype=np.int32)
         starts = (np.cumsum(counts_p) - counts_p).astype(np.int32)
         ctx_p = np.asarray(ctx_len + [0] * pad_rows, dtype=np.int32)

@@ -35,6 +35,7 @@ _STATUS_TEXT = {
 }
 
 _lib: Optional[ctypes.CDLL] = None
+LAUNCHES = 0        # kernels of this library launched so far (bench.py reports the count)
 
 
 class KernelError(RuntimeError):
@@ -86,9 +87,11 @@ def _declare(L: ctypes.CDLL) -> None:
     L.fd_attn_scratch_floats.restype = LL
 
 
-def _check(rc: int) -> None:
+def _check(rc: int, kernels: int = 1) -> None:
+    global LAUNCHES
     if rc != 0:
         raise KernelError(lib().fd_last_error().decode())
+    LAUNCHES += kernels
 
 
 def _stream() -> int:
@@ -209,7 +212,8 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
                                    _ptr(block_table), block_table.shape[1], num_blocks, block_size,
                                    _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len),
                                    _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale),
-                                   int(window), n_splits, split_len, _ptr(scratch), _ptr(status), _stream()))
+                                   int(window), n_splits, split_len, _ptr(scratch), _ptr(status), _stream()),
+           kernels=2 if n_splits > 1 else 1)
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
