@@ -132,7 +132,8 @@ def ragged_prompts(batch: int, lo: int, hi: int, vocab: int, seed: int):
     return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
 
 
-def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: int, e2e: bool):
+def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: int, e2e: bool,
+               prompt_range=None, profile: bool = False):
     """Prefill ragged prompts, decode untimed until ``steps + warmup`` steps are
     left before the longest sequence reaches ``context``, then time."""
     import torch
@@ -140,7 +141,8 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
     from flashdecode_cuda_b200.engine.decode import GraphDecoder
     model = engine.model
     vocab = model.vocab_size
-    prompts = ragged_prompts(batch, context // 4, context // 2, vocab, seed)
+    lo, hi = prompt_range or (context // 4, context // 2)
+    prompts = ragged_prompts(batch, lo, hi, vocab, seed)
     cache = model.new_cache(batch_size=batch, max_len=context, block_size=16)
     out = {}
     if e2e:
@@ -175,11 +177,15 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
     kv_start = cache.kv_bytes(slots)
     K.LAUNCHES = 0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if profile:
+        torch.cuda.profiler.start()       # for `ncu --profile-from-start off`: only the timed steps are seen
     start.record()
     for _ in range(steps):
         dec.run(slots, None)
     end.record()
     torch.cuda.synchronize()
+    if profile:
+        torch.cuda.profiler.stop()
     ms = start.elapsed_time(end) / steps
     kv_end = cache.kv_bytes(slots)
     model.check_status()
@@ -229,6 +235,11 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64, prefill and e2e")
+    ap.add_argument("--prompt-min", type=int, default=0, help="shortest prompt (default context/4)")
+    ap.add_argument("--prompt-max", type=int, default=0, help="longest prompt (default context/2)")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill measurement")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -246,7 +257,14 @@ def main() -> int:
     engine, cfg, full_layers = build_engine(args.preset, args.layers, args.seed)
     clocks = ClockSampler()
     clocks.start()
-    main_run = decode_run(engine, args.batch, args.context, args.steps, warmup, args.seed, e2e=False)
+    if args.prefill_only:
+        if args.profile_range:
+            torch.cuda.profiler.start()
+        print(json.dumps({"prefill": prefill_run(engine, cfg, 2048, 1 if args.profile_range else warmup, args.seed, pk)}))
+        return 0
+    prange = (args.prompt_min or args.context // 4, args.prompt_max or args.context // 2)
+    main_run = decode_run(engine, args.batch, args.context, args.steps, warmup, args.seed, e2e=False,
+                          prompt_range=prange, profile=args.profile_range)
     points, prefill, e2e = {}, None, None
     if not args.no_points:
         e2e = decode_run(engine, args.batch, args.context, args.steps, warmup, args.seed, e2e=True)
@@ -272,7 +290,7 @@ def main() -> int:
             "model": args.preset, "layers": cfg.num_hidden_layers, "layers_full": full_layers,
             "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-            "global_batch": args.batch, "seq_len": args.context, "prompt_lens": "uniform[1024,2048]",
+            "global_batch": args.batch, "seq_len": args.context, "prompt_lens": "uniform[%d,%d]" % prange,
             "mean_context": round(main_run["mean_context"], 1), "block_size": 16, "parallelism": "1 GPU",
             "l2": "each step reads %.2f GB, far beyond the 126 MB L2; no flush needed" % (step_bytes / 1e9),
             "peaks": pk["source"],

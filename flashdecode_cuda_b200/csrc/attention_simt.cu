@@ -18,7 +18,7 @@
 // fallback for head sizes the tensor-core kernels do not take.
 #include <math.h>
 
-#include "common.cuh"
+#include "attention.cuh"
 
 namespace fd {
 
@@ -29,25 +29,6 @@ constexpr int RMAX = 64;        // query rows per CTA
 constexpr int RPW = RMAX / ATT_WARPS;   // rows per warp in the score phase
 constexpr int RPT_MAX = 16;     // rows per thread in the value phase
 
-struct AttnParams {
-    const void* q;             // [T, n_q * d]
-    const void* k_pool;        // [num_blocks, n_kv, block_size, d]
-    const void* v_pool;
-    void* out;                 // [T, n_q * d]
-    float* part_m;             // [T, n_q, n_splits]
-    float* part_l;
-    float* part_acc;           // [T, n_q, n_splits, d]
-    const int* block_table;    // [slots, max_blocks]
-    const int* row_slot;       // per batch row: cache slot, or -1 for a padding row
-    const int* row_q_start;    // first token of the row in the flat token arrays
-    const int* row_q_len;      // new tokens of the row in this step
-    const int* row_ctx_len;    // tokens of the row cached before this step
-    int* status;
-    int max_blocks, num_blocks, block_size;
-    int n_q, n_kv, G, d;
-    int QT, n_splits, split_len, window;
-    float scale;
-};
 
 template <typename T> struct Pad;            // padding of a key row in shared memory, in elements
 template <> struct Pad<float> { static constexpr int v = 4; };
@@ -328,13 +309,15 @@ extern "C" long long fd_attn_scratch_floats(int T, int n_q, int d, int n_splits)
 // dtype: 0 = float32, 1 = bfloat16 (queries, cache and output alike).
 // n_splits == 1 writes `out` directly; otherwise `scratch` must hold
 // fd_attn_scratch_floats(T, ...) floats and the merge kernel runs after.
-extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
-                                 const int* block_table, int max_blocks, int num_blocks, int block_size,
-                                 const int* tok_row, const int* row_slot, const int* row_q_start,
-                                 const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
-                                 int max_q_len, int n_q, int n_kv, int d, float scale, int window,
-                                 int n_splits, int split_len, float* scratch, int* status,
-                                 cudaStream_t stream) {
+// use_mma != 0: decode steps (max_q_len == 1) in bfloat16 go to the
+// tensor-core kernel when it takes the head size and group size.
+static int attention_impl(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
+                          const int* block_table, int max_blocks, int num_blocks, int block_size,
+                          const int* tok_row, const int* row_slot, const int* row_q_start,
+                          const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
+                          int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                          int n_splits, int split_len, float* scratch, int* status, int use_mma,
+                          cudaStream_t stream) {
     if (n_rows == 0 || T == 0) return 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
@@ -345,8 +328,9 @@ extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* 
     FD_REQUIRE(n_splits == 1 || (split_len > 0 && split_len % KT == 0), -2,
                "attention: split length %d must be a positive multiple of %d", split_len, KT);
     FD_REQUIRE(n_splits == 1 || scratch != nullptr, -2, "attention: split form needs scratch memory");
-    FD_REQUIRE((uintptr_t)scratch % 16 == 0 && (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0, -2,
-               "attention: the cache pools and the scratch memory must be 16-byte aligned");
+    FD_REQUIRE((uintptr_t)scratch % 16 == 0 && (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 &&
+               (uintptr_t)q % 16 == 0, -2,
+               "attention: queries, cache pools and scratch memory must be 16-byte aligned");
     FD_REQUIRE(n_splits == 1 || T <= 65535, -2, "attention: the split form takes at most 65535 tokens, got %d", T);
     FD_REQUIRE(n_rows <= 65535 && n_kv <= 65535, -2, "attention: batch of %d rows too large", n_rows);
 
@@ -365,7 +349,10 @@ extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* 
     if (qt > max_q_len) qt = max_q_len;
     p.QT = qt; p.n_splits = n_splits; p.split_len = split_len; p.window = window; p.scale = scale;
 
-    int rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
+    int rc = 1;
+    if (use_mma && dtype == 1 && max_q_len == 1) rc = launch_attn_decode_mma(p, n_rows, stream);
+    if (rc == 1)
+        rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
                         : launch_attn<bf16>(p, n_rows, max_q_len, stream);
     if (rc != 0 || n_splits == 1) return rc;
     dim3 grid(n_q, T);
@@ -376,4 +363,30 @@ extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* 
         attn_combine_kernel<bf16><<<grid, 128, 0, stream>>>(p.part_m, p.part_l, p.part_acc, (bf16*)out,
                                                            tok_row, row_slot, n_q, d, n_splits);
     return check_launch("attention_combine");
+}
+
+// The CUDA-core kernel for every case.
+extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
+                                 const int* block_table, int max_blocks, int num_blocks, int block_size,
+                                 const int* tok_row, const int* row_slot, const int* row_q_start,
+                                 const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
+                                 int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                                 int n_splits, int split_len, float* scratch, int* status,
+                                 cudaStream_t stream) {
+    return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
+                          row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
+                          window, n_splits, split_len, scratch, status, 0, stream);
+}
+
+// The fastest kernel that takes the sizes: tensor cores where possible.
+extern "C" int fd_attention(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
+                            const int* block_table, int max_blocks, int num_blocks, int block_size,
+                            const int* tok_row, const int* row_slot, const int* row_q_start,
+                            const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
+                            int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                            int n_splits, int split_len, float* scratch, int* status,
+                            cudaStream_t stream) {
+    return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
+                          row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
+                          window, n_splits, split_len, scratch, status, 1, stream);
 }

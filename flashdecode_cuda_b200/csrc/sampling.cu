@@ -28,18 +28,25 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
     return v > bv || (v == bv && i < bi);
 }
 
-// One CTA per row.  temperature[row] <= 0 means greedy.
-__global__ void __launch_bounds__(512)
-sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
-              const long long* __restrict__ request, const int* __restrict__ step,
-              unsigned long long seed, int* __restrict__ out) {
-    const int row = blockIdx.x;
+constexpr int SAMPLE_CHUNK = 4096;      // vocabulary entries per CTA (a multiple of 4: one Philox call gives 4)
+constexpr int SAMPLE_THREADS = 256;
+
+// Score of vocabulary entry i of a row: the logit (greedy) or logit / T + Gumbel noise.
+// A CTA scans one chunk of one row and keeps the best (score, index), the
+// lowest index winning ties; temperature[row] <= 0 means greedy.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_partial_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+                      const long long* __restrict__ request, const int* __restrict__ step,
+                      unsigned long long seed, float* __restrict__ part_v, int* __restrict__ part_i,
+                      int* __restrict__ out, int n_chunks) {
+    const int row = blockIdx.y, chunk = blockIdx.x;
     const float* x = logits + (size_t)row * V;
     const float temp = temperature ? temperature[row] : 0.f;
+    const int begin = chunk * SAMPLE_CHUNK, end = min(V, begin + SAMPLE_CHUNK);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     if (temp <= 0.f) {
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        for (int i = begin + threadIdx.x; i < end; i += SAMPLE_THREADS) {
             const float v = x[i];
             if (better(v, i, bv, bi)) { bv = v; bi = i; }
         }
@@ -47,13 +54,13 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
         const unsigned long long rq = (unsigned long long)request[row];
         const uint32_t st = (uint32_t)step[row];
         const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
-        for (int j = threadIdx.x; j * 4 < V; j += blockDim.x) {
+        for (int j = begin / 4 + threadIdx.x; j * 4 < end; j += SAMPLE_THREADS) {
             uint32_t r[4];
             philox4x32_10((uint32_t)j, st, (uint32_t)rq, (uint32_t)(rq >> 32), k0, k1, r);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int i = j * 4 + e;
-                if (i < V) {
+                if (i < end) {
                     const float u = ((float)(r[e] >> 9) + 0.5f) * (1.0f / 8388608.0f);
                     const float v = x[i] / temp + (-logf(-logf(u)));
                     if (better(v, i, bv, bi)) { bv = v; bi = i; }
@@ -61,45 +68,87 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
             }
         }
     }
-    // block argmax
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
         if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
-    __shared__ float sv[32];
-    __shared__ int si[32];
+    __shared__ float sv[SAMPLE_THREADS / 32];
+    __shared__ int si[SAMPLE_THREADS / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
-        const int nw = blockDim.x >> 5;
-        bv = lane < nw ? sv[lane] : -INFINITY;
-        bi = lane < nw ? si[lane] : 0x7fffffff;
+        bv = lane < SAMPLE_THREADS / 32 ? sv[lane] : -INFINITY;
+        bi = lane < SAMPLE_THREADS / 32 ? si[lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+        if (lane == 0) {
+            if (n_chunks == 1) {
+                out[row] = bi == 0x7fffffff ? 0 : bi;
+            } else {
+                part_v[(size_t)row * n_chunks + chunk] = bv;
+                part_i[(size_t)row * n_chunks + chunk] = bi;
+            }
+        }
     }
+}
+
+// One warp per row merges the chunks' winners.
+__global__ void sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int n_chunks, int* __restrict__ out) {
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = lane; c < n_chunks; c += 32) {
+        const float v = part_v[(size_t)row * n_chunks + c];
+        const int i = part_i[(size_t)row * n_chunks + c];
+        if (better(v, i, bv, bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
 }
 
 }  // namespace fd
 
 using namespace fd;
 
+// 4-byte words of scratch that fd_sample needs for n rows of V logits.
+extern "C" long long fd_sample_scratch_words(int n, int V) {
+    const long long chunks = (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    return chunks > 1 ? 2 * chunks * n : 0;
+}
+
 // logits [n, V] float; temperature [n] float or null (all greedy); request [n]
-// int64 and step [n] int32 (needed when any temperature is > 0); out [n] int32.
+// int64 and step [n] int32 (needed when any temperature is > 0); out [n] int32;
+// scratch: fd_sample_scratch_words(n, V) words (may be null when that is 0).
 extern "C" int fd_sample(const float* logits, int n, int V, const float* temperature,
                          const long long* request, const int* step, unsigned long long seed, int* out,
-                         cudaStream_t stream) {
+                         void* scratch, cudaStream_t stream) {
     if (n == 0) return 0;
     FD_REQUIRE(V > 0, -2, "sample: vocabulary %d", V);
+    FD_REQUIRE(n <= 65535, -2, "sample: %d rows in one call", n);
     FD_REQUIRE(temperature == nullptr || (request != nullptr && step != nullptr), -2,
                "sample: temperature sampling needs request ids and step counters");
-    sample_kernel<<<n, 512, 0, stream>>>(logits, V, temperature, request, step, seed, out);
-    return check_launch("sample");
+    const int chunks = (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    FD_REQUIRE(chunks == 1 || scratch != nullptr, -2, "sample: a vocabulary of %d needs scratch memory", V);
+    float* part_v = (float*)scratch;
+    int* part_i = (int*)scratch + (size_t)chunks * n;
+    dim3 grid(chunks, n);
+    sample_partial_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, request, step, seed,
+                                                             part_v, part_i, out, chunks);
+    int rc = check_launch("sample");
+    if (rc != 0 || chunks == 1) return rc;
+    sample_final_kernel<<<n, 32, 0, stream>>>(part_v, part_i, chunks, out);
+    return check_launch("sample_final");
 }

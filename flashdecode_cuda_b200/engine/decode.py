@@ -44,6 +44,7 @@ class _Graph:
         self.sampled: Optional[torch.Tensor] = None
         self.temp = self.req = self.step = None
         self.launches = 0
+        self.sample_scratch = None
 
 
 class GraphDecoder:
@@ -72,9 +73,9 @@ class GraphDecoder:
     def _body(self, g: _Graph, ctx: StepContext, key: Tuple) -> None:
         logits = self.model.forward(ctx)
         if key[2]:
-            K.sample(logits, g.sampled)
+            K.sample(logits, g.sampled, scratch=g.sample_scratch)
         else:
-            K.sample(logits, g.sampled, g.temp, g.req, g.step, key[3])
+            K.sample(logits, g.sampled, g.temp, g.req, g.step, key[3], scratch=g.sample_scratch)
 
     def _graph_for(self, key: Tuple, slots, tokens) -> Tuple[_Graph, StepContext]:
         g = self.graphs.get(key)
@@ -87,6 +88,8 @@ class GraphDecoder:
         g.temp = torch.zeros(B, dtype=torch.float32, device=dev)
         g.req = torch.zeros(B, dtype=torch.int64, device=dev)
         g.step = torch.zeros(B, dtype=torch.int32, device=dev)
+        g.sample_scratch = torch.zeros(max(1, K.sample_scratch_words(B, self.model.vocab_size)),
+                                       dtype=torch.int32, device=dev)
         ctx = self._prepare(g, key, slots, tokens)
         # one eager run: it allocates the workspace and writes this step's keys
         # and values; the captured replay below rewrites the same values

@@ -77,7 +77,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
         "fd_attn_simt_qt": [I],
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
-        "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P],
+        "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
+        "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)
@@ -85,6 +86,8 @@ def _declare(L: ctypes.CDLL) -> None:
         fn.restype = I
     L.fd_attn_scratch_floats.argtypes = [I, I, I, I]
     L.fd_attn_scratch_floats.restype = LL
+    L.fd_sample_scratch_words.argtypes = [I, I]
+    L.fd_sample_scratch_words.restype = LL
 
 
 def _check(rc: int, kernels: int = 1) -> None:
@@ -195,20 +198,16 @@ def attention_scratch_floats(n_tokens: int, n_q: int, head_dim: int, n_splits: i
     return int(lib().fd_attn_scratch_floats(n_tokens, n_q, head_dim, n_splits))
 
 
-def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
-                   block_table: torch.Tensor, tok_row: torch.Tensor, row_slot: torch.Tensor,
-                   row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
-                   n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
-                   window: int = 0, n_splits: int = 1, split_len: int = 0,
-                   scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
-    """Causal GQA attention of the step's tokens over the paged cache."""
+def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
+               row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
+               scratch, status) -> None:
     T = q.shape[0]
     num_blocks, _, block_size, _ = k_pool.shape
     assert q.dtype == k_pool.dtype == out.dtype
     if n_splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32
         assert scratch.numel() >= attention_scratch_floats(T, n_q, head_dim, n_splits)
-    _check(lib().fd_attention_simt(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype),
+    _check(getattr(lib(), fn_name)(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype),
                                    _ptr(block_table), block_table.shape[1], num_blocks, block_size,
                                    _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len),
                                    _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale),
@@ -216,12 +215,58 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
            kernels=2 if n_splits > 1 else 1)
 
 
+def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+              block_table: torch.Tensor, tok_row: torch.Tensor, row_slot: torch.Tensor,
+              row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
+              n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
+              window: int = 0, n_splits: int = 1, split_len: int = 0,
+              scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """Causal GQA attention of the step's tokens over the paged cache, by the
+    fastest kernel that takes the sizes (tensor cores for bfloat16 decode steps
+    with head size 64 or 128; the CUDA-core kernel otherwise)."""
+    _attention("fd_attention", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
+               row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
+               scratch, status)
+
+
+def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                   block_table: torch.Tensor, tok_row: torch.Tensor, row_slot: torch.Tensor,
+                   row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
+                   n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
+                   window: int = 0, n_splits: int = 1, split_len: int = 0,
+                   scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """The same on the CUDA cores for every size (the true 32-bit path)."""
+    _attention("fd_attention_simt", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start,
+               row_q_len, row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits,
+               split_len, scratch, status)
+
+
+_sample_scratch = {}
+
+
+def sample_scratch_words(n: int, V: int) -> int:
+    return int(lib().fd_sample_scratch_words(n, V))
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
-           request: Optional[torch.Tensor] = None, step: Optional[torch.Tensor] = None, seed: int = 0) -> None:
-    """out[i] = argmax (greedy) or a Gumbel-max draw from softmax(logits[i] / T_i)."""
+           request: Optional[torch.Tensor] = None, step: Optional[torch.Tensor] = None, seed: int = 0,
+           scratch: Optional[torch.Tensor] = None) -> None:
+    """out[i] = argmax (greedy) or a Gumbel-max draw from softmax(logits[i] / T_i).
+    ``scratch``: int32 tensor of ``sample_scratch_words(n, V)`` entries for large
+    vocabularies; when omitted a per-device buffer is kept and reused."""
     n, V = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32
     if temperature is not None:
         assert temperature.dtype == torch.float32 and request.dtype == torch.int64 and step.dtype == torch.int32
+    words = sample_scratch_words(n, V)
+    if words and scratch is None:
+        key = logits.device
+        scratch = _sample_scratch.get(key)
+        if scratch is None or scratch.numel() < words:
+            scratch = torch.empty(max(words, 4096), dtype=torch.int32, device=logits.device)
+            _sample_scratch[key] = scratch
+    if words:
+        assert scratch.dtype == torch.int32 and scratch.numel() >= words
     _check(lib().fd_sample(_ptr(logits), n, V, _ptr(temperature), _ptr(request), _ptr(step),
-                           seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _stream()))
+                           seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _ptr(scratch) if words else None, _stream()),
+           kernels=2 if words else 1)

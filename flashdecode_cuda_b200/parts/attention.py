@@ -98,7 +98,7 @@ class GQAAttention(Mixer):
             if n_splits > 1:
                 scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, self.n_q, d, n_splits),),
                                  torch.float32)
-        K.attention_simt(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot,
+        K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot,
                          ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len,
                          self.n_q, self.n_kv, d, self.scale, self.window or 0, n_splits, split_len, scratch,
                          self.rt.status)

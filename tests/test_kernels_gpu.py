@@ -237,7 +237,7 @@ def attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window
 
 
 def run_attention(dtype, n_q, n_kv, d, bs, ctx, new, window=0, n_splits=1, split_len=0, seed=7,
-                  spike=None, pad_rows=0):
+                  spike=None, pad_rows=0, fn=None):
     g = torch.Generator().manual_seed(seed)
     dt = DT[dtype]
     lens = [c + n for c, n in zip(ctx, new)]
@@ -266,7 +266,7 @@ def run_attention(dtype, n_q, n_kv, d, bs, ctx, new, window=0, n_splits=1, split
         scratch = torch.full((K.attention_scratch_floats(Tp, n_q, d, n_splits),), float("nan"), device=DEV)
     st = status()
     scale = 1.0 / math.sqrt(d)
-    K.attention_simt(qp, kp, vp, out, table.to(DEV), tok_row, i32(slots_p), i32(starts), i32(new_p), i32(ctx_p),
+    (fn or K.attention_simt)(qp, kp, vp, out, table.to(DEV), tok_row, i32(slots_p), i32(starts), i32(new_p), i32(ctx_p),
                      rows, max(new_p), n_q, n_kv, d, scale, window, n_splits, split_len, scratch, st)
     assert int(st.item()) == 0
     want = attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window)
@@ -324,6 +324,31 @@ def test_attention_far_key_stands_out(dtype):
         assert rel(got, want) < TOL[dtype], key_pos
         got, want, _ = run_attention(dtype, 6, 2, 64, 16, ctx=[0, 0], new=[700, 3], spike=(0, key_pos))
         assert rel(got, want) < TOL[dtype], key_pos
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,bs", [(12, 2, 128, 16), (7, 1, 128, 4), (5, 5, 64, 32), (16, 1, 64, 16),
+                                           (28, 4, 128, 16), (40, 8, 128, 8), (3, 3, 128, 1)])
+@pytest.mark.parametrize("n_splits,split_len", [(1, 0), (3, 128), (11, 32)])
+def test_attention_decode_tensor_cores(n_q, n_kv, d, bs, n_splits, split_len):
+    """The dispatcher's tensor-core kernel for bfloat16 decode steps: groups that
+    are no power of two, cached lengths at tile and split edges, a padding row."""
+    ctx = [0, 15, 16, 17, 127, 128, 300, 63]
+    got, want, pad = run_attention("bfloat16", n_q, n_kv, d, bs, ctx=ctx, new=[1] * len(ctx),
+                                   n_splits=n_splits, split_len=split_len, pad_rows=1, fn=K.attention)
+    assert rel(got, want) < TOL["bfloat16"]
+    if n_splits > 1:
+        assert float(pad.float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("window", [1, 16, 17, 100])
+def test_attention_decode_tensor_cores_window_and_far_key(window):
+    got, want, _ = run_attention("bfloat16", 6, 2, 128, 16, ctx=[200, 40, 7], new=[1, 1, 1], window=window,
+                                 n_splits=4, split_len=64, fn=K.attention)
+    assert rel(got, want) < TOL["bfloat16"]
+    for key_pos in (0, 15, 16, 255, 256, 511, 698):
+        got, want, _ = run_attention("bfloat16", 12, 2, 128, 16, ctx=[699, 40], new=[1, 1], n_splits=6,
+                                     split_len=128, spike=(0, key_pos), fn=K.attention)
+        assert rel(got, want) < TOL["bfloat16"], key_pos
 
 
 def test_attention_refuses_what_it_cannot_do():
