@@ -48,7 +48,8 @@ class Engine(Backend):
         self.sampler = Sampler(model.device)
         self.cache: Optional[PagedCache] = None
         self.seed = 0
-        self.use_graphs = model.device.type == "cuda"     # decode steps replay captured CUDA graphs
+        # decode steps replay captured CUDA graphs unless a part decides on the host
+        self.use_graphs = model.device.type == "cuda" and model.graph_safe
         self._graph_decoder: Optional[GraphDecoder] = None
 
     # -- caches -----------------------------------------------------------

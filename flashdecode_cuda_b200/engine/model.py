@@ -191,6 +191,11 @@ class Model:
         self.bound = True
         return self
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether decode steps may be captured into CUDA graphs (every part says so)."""
+        return all(getattr(p, "graph_safe", True) for p in self.all_parts())
+
     def weight_bytes(self, include_embedding: bool = False) -> int:
         """Bytes of weights a decode step reads once: every layer's matrices
         and vectors and the output head; the embedding table only by rows."""

@@ -70,6 +70,9 @@ class LayerCache:
 
 class Part:
     kind = ""
+    # False for a part whose forward reads the step's host mirrors (``ctx.h_*``) or
+    # otherwise decides on the host: its steps cannot be replayed from a CUDA graph.
+    graph_safe = True
 
     def tensor_specs(self) -> List[TensorSpec]:
         return []

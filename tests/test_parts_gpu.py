@@ -1,0 +1,273 @@
+"""Each part alone against the plain function of the same name, and a toy
+architecture defined here - a mixer with fixed-size state of its own, mixed
+with attention layers, one layer run twice, one entry reading another's cache -
+registered, built and stepped without touching the framework's files."""
+
+import json
+import math
+from dataclasses import dataclass
+from typing import Dict, List
+
+import pytest
+import torch
+
+import flashdecode_cuda_b200 as fd
+from flashdecode_cuda_b200.cache import StateSpec
+from flashdecode_cuda_b200.engine import LayerSpec, Model, ModelBlueprint, PartSpec, RunSpec
+from flashdecode_cuda_b200.parts import LayerCache, Mixer
+from flashdecode_cuda_b200.weights import TensorSpec
+from helpers import TINY, TOL, prompts_for, raw_config, rel_err, weights_of, write_folder
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+PART_TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    return write_folder(tmp_path_factory.mktemp("parts"), "C", seed=4)
+
+
+def setup(folder, dtype, lengths):
+    eng = fd.load(folder, device="cuda", dtype=dtype)
+    model = eng.model
+    cache = model.new_cache(max_tokens=512, block_size=8)
+    prompts = prompts_for(TINY["C"]["vocab_size"], lengths, seed=2)
+    slots = [cache.admit() for _ in prompts]
+    cache.reserve([(s, len(p)) for s, p in zip(slots, prompts)])
+    cache.sync()
+    ctx = model.make_context(cache, slots, prompts, "all")
+    return model, cache, ctx, prompts
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_norm_feed_forward_head(folder, dtype):
+    model, cache, ctx, prompts = setup(folder, dtype, [9, 30])
+    raw, w = raw_config(folder), {k: v.double() for k, v in weights_of(folder).items()}
+    T, H = ctx.T, model.hidden_size
+    flat = [t for p in prompts for t in p]
+    resid = torch.empty(T, H, device="cuda")
+    model.embedding.forward(ctx, resid)
+    assert torch.equal(resid.cpu().double(), P.embedding(torch.tensor(flat), w["model.embed_tokens.weight"]))
+
+    g = torch.Generator().manual_seed(0)
+    delta = torch.randn(T, H, generator=g).to(DT[dtype]).cuda()
+    before = resid.clone()
+    xn = torch.empty(T, H, dtype=DT[dtype], device="cuda")
+    norm = model.blocks[1].norm2
+    norm.forward(ctx, delta, resid, xn)
+    summed = before.double().cpu() + delta.double().cpu()
+    assert rel_err(resid, summed) < 1e-6
+    want = P.rmsnorm(summed, w["model.layers.1.post_attention_layernorm.weight"], raw["rms_norm_eps"])
+    assert rel_err(xn, want) < PART_TOL[dtype]
+
+    x = (0.5 * torch.randn(T, H, generator=g)).to(DT[dtype]).cuda()
+    got = model.blocks[2].feed_forward.forward(ctx, x)
+    assert rel_err(got, P.mlp_block(w, 2, x.double().cpu())) < PART_TOL[dtype]
+
+    logits = model.head.forward(ctx, x[:5].contiguous())
+    assert logits.dtype == torch.float32
+    assert rel_err(logits, P.linear(x[:5].double().cpu(), w["lm_head.weight"])) < PART_TOL[dtype]
+
+
+def test_rotary_tables(folder):
+    model, cache, ctx, _ = setup(folder, "float32", [3])
+    rope = model.positions["rope"]
+    cos, sin = P.rope_tables(TINY["C"]["head_dim"], rope.cos.shape[0], TINY["C"]["rope_theta"])
+    half = TINY["C"]["head_dim"] // 2
+    assert torch.equal(rope.cos.cpu(), cos[:, :half]) and torch.equal(rope.sin.cpu(), sin[:, :half])
+    assert rope.cos.shape[0] == cache.max_len
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layer", [0, 3])           # full attention, and a window of 24
+def test_attention_mixer_and_block(folder, dtype, layer):
+    lengths = [9, 30, 41]
+    model, cache, ctx, prompts = setup(folder, dtype, lengths)
+    raw, w = raw_config(folder), {k: v.double() for k, v in weights_of(folder).items()}
+    T, H = ctx.T, model.hidden_size
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(T, H, generator=g).to(DT[dtype]).cuda()
+    lc = model._layer_caches(cache)[layer]
+    got = model.blocks[layer].mixer.forward(ctx, x, lc)
+    cos, sin = P.rope_tables(raw["head_dim"], max(lengths), raw["rope_theta"])
+    o = 0
+    for n in lengths:
+        want = P.attention_block(raw, w, layer, x[o:o + n].double().cpu(), cos[:n], sin[:n])
+        assert rel_err(got[o:o + n], want) < PART_TOL[dtype]
+        o += n
+    # the whole arrangement: x += mixer(norm(x)); x += ff(norm(x)), handed on as (resid, delta)
+    resid = x.float().clone()
+    delta = model.blocks[layer].forward(ctx, resid, None, lc)
+    o = 0
+    for n in lengths:
+        xs = x[o:o + n].double().cpu()
+        p = f"model.layers.{layer}"
+        mid = xs + P.attention_block(raw, w, layer, P.rmsnorm(xs, w[f"{p}.input_layernorm.weight"], raw["rms_norm_eps"]),
+                                     cos[:n], sin[:n])
+        ff = P.mlp_block(w, layer, P.rmsnorm(mid, w[f"{p}.post_attention_layernorm.weight"], raw["rms_norm_eps"]))
+        assert rel_err(resid[o:o + n], mid) < PART_TOL[dtype]
+        assert rel_err(delta[o:o + n], ff) < 2 * PART_TOL[dtype]
+        o += n
+    model.check_status()
+
+
+# ---------------------------------------------------------------------------
+# a toy architecture, defined and registered here
+# ---------------------------------------------------------------------------
+
+@fd.register_part("mixer", "toy_running_mean")
+class RunningMean(Mixer):
+    """delta_t = W * mean(x_0 .. x_t): its cache is one running sum per
+    sequence (fixed size), not keys.  Written with torch on the device and the
+    step's host mirrors, so its steps are not replayed from CUDA graphs."""
+    graph_safe = False
+
+    def __init__(self, prefix, hidden_size):
+        self.prefix, self.H = prefix, hidden_size
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.mix.weight", (self.H, self.H))]
+
+    def state_requests(self):
+        return [StateSpec("sum", (self.H,), torch.float32)]
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.w = tensors[f"{self.prefix}.mix.weight"]
+
+    def forward(self, ctx, x, lc: LayerCache):
+        out = ctx.ws.get("toy_out", tuple(x.shape), x.dtype)
+        state = lc.states["sum"]
+        o = 0
+        for slot, n, cached in zip(ctx.h_slots, ctx.h_q_len, ctx.h_ctx_len):
+            sums = torch.cumsum(x[o:o + n].float(), 0) + state[slot]
+            counts = torch.arange(cached + 1, cached + n + 1, device=x.device, dtype=torch.float32)
+            out[o:o + n] = ((sums / counts[:, None]) @ self.w.float().T).to(x.dtype)
+            if lc.writes:
+                state[slot] = sums[-1]
+            o += n
+        return out
+
+
+@dataclass
+class ToyConfig:
+    hidden_size: int
+    vocab_size: int
+    intermediate_size: int
+    eps: float
+    architecture: str = "ToyForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["hidden_size"], d["vocab_size"], d["intermediate_size"], d["eps"])
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                "intermediate_size": self.intermediate_size, "eps": self.eps}
+
+
+def toy_blueprint(cfg: ToyConfig) -> ModelBlueprint:
+    H = cfg.hidden_size
+
+    def layer(i, mixer):
+        p = f"toy.layers.{i}"
+        return LayerSpec("prenorm", PartSpec("norm", "rmsnorm", dict(size=H, eps=cfg.eps), f"{p}.n1"), mixer,
+                         PartSpec("norm", "rmsnorm", dict(size=H, eps=cfg.eps), f"{p}.n2"),
+                         PartSpec("feed_forward", "swiglu", dict(hidden_size=H, intermediate_size=cfg.intermediate_size),
+                                  f"{p}.ff"))
+    attn = lambda i: PartSpec("mixer", "gqa_attention", dict(hidden_size=H, n_heads=2, n_kv_heads=1, head_dim=16,
+                                                            position="rope", bias=False), f"toy.layers.{i}.attn")
+    return ModelBlueprint(
+        hidden_size=H, vocab_size=cfg.vocab_size,
+        embedding=PartSpec("embedding", "token_table", dict(vocab_size=cfg.vocab_size, hidden_size=H), "toy.embed"),
+        positions={"rope": PartSpec("position", "rotary_half", dict(head_dim=16, theta=100.0, max_positions=256))},
+        layers=[layer(0, PartSpec("mixer", "toy_running_mean", dict(hidden_size=H), "toy.layers.0")),
+                layer(1, attn(1)),
+                layer(2, PartSpec("mixer", "toy_running_mean", dict(hidden_size=H), "toy.layers.2"))],
+        # layer 0 runs twice (shared weights, separate state); the last entry reads the keys of entry 1
+        schedule=[RunSpec(0), RunSpec(1), RunSpec(2), RunSpec(0), RunSpec(1, cache_from=1)],
+        final_norm=PartSpec("norm", "rmsnorm", dict(size=H, eps=cfg.eps), "toy.norm"),
+        head=PartSpec("head", "linear_head", dict(vocab_size=cfg.vocab_size, hidden_size=H, tied_to="toy.embed.weight"),
+                      "toy.head"),
+        max_positions=256)
+
+
+fd.register_architecture("ToyForCausalLM", ToyConfig, toy_blueprint)
+
+
+def toy_plain(w: Dict[str, torch.Tensor], cfg: ToyConfig, tokens: List[int]) -> torch.Tensor:
+    """The toy model on one whole sequence, in float64, with the plain parts."""
+    w = {k: v.double() for k, v in w.items()}
+    x = w["toy.embed.weight"][torch.tensor(tokens)]
+    S = len(tokens)
+    cos, sin = P.rope_tables(16, S, 100.0)
+    kept = {}
+
+    def ff(i, h):
+        p = f"toy.layers.{i}.ff"
+        return P.linear(P.swiglu(P.linear(h, w[f"{p}.gate_proj.weight"]), P.linear(h, w[f"{p}.up_proj.weight"])),
+                        w[f"{p}.down_proj.weight"])
+
+    def mean_mixer(i, h):
+        means = torch.cumsum(h, 0) / torch.arange(1, S + 1, dtype=torch.float64)[:, None]
+        return means @ w[f"toy.layers.{i}.mix.weight"].T
+
+    def attn(i, h, own_kv):
+        p = f"toy.layers.{i}.attn"
+        q = P.apply_rope(P.linear(h, w[f"{p}.q_proj.weight"]).view(S, 2, 16), cos, sin)
+        if own_kv:
+            k = P.apply_rope(P.linear(h, w[f"{p}.k_proj.weight"]).view(S, 1, 16), cos, sin)
+            kept[i] = (k, P.linear(h, w[f"{p}.v_proj.weight"]).view(S, 1, 16))
+        k, v = kept[i]
+        o = P.causal_gqa_attention(q, k, v, 1 / math.sqrt(16), None)
+        return P.linear(o.reshape(S, 32), w[f"{p}.o_proj.weight"])
+
+    for layer, own in [(0, True), (1, True), (2, True), (0, True), (1, False)]:
+        p = f"toy.layers.{layer}"
+        h = P.rmsnorm(x, w[f"{p}.n1.weight"], cfg.eps)
+        x = x + (attn(layer, h, own) if layer == 1 else mean_mixer(layer, h))
+        x = x + ff(layer, P.rmsnorm(x, w[f"{p}.n2.weight"], cfg.eps))
+    return P.rmsnorm(x, w["toy.norm.weight"], cfg.eps) @ w["toy.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
+    cfg = ToyConfig(48, 101, 80, 1e-5)
+    folder = tmp_path / "toy"
+    probe = Model.from_config(cfg, torch.float32, "cpu")
+    tensors = fd.weights.random_tensors(probe.tensor_specs(), 3)
+    fd.weights.write_model_folder(folder, cfg.to_dict(), tensors)
+
+    eng = fd.load(folder, device="cuda", dtype=dtype)         # chosen by config.json, like any model
+    model = eng.model
+    assert isinstance(model.blocks[0].mixer, RunningMean) and not model.graph_safe and not eng.use_graphs
+    groups = model.cache_groups()
+    assert len(groups) == 1 and groups[0].n_layers == 1       # entry 4 shares entry 1's keys
+    cache = model.new_cache(max_tokens=256, block_size=8)
+    assert sorted(cache.states) == ["run0.sum", "run2.sum", "run3.sum"]
+
+    prompts = prompts_for(101, [23, 5, 40], seed=1)
+    want = [toy_plain(tensors, cfg, p) for p in prompts]
+    # whole prompts in one unequal batch
+    slots = [cache.admit() for _ in prompts]
+    got = model.step(cache, slots, prompts, "all")
+    o = 0
+    for p, ref in zip(prompts, want):
+        assert rel_err(got[o:o + len(p)], ref) < TOL[dtype]
+        o += len(p)
+    for s in slots:
+        cache.release(s)
+    # a cut prompt, then token by token, in slots that are used again (state must start from zero)
+    slots = [cache.admit() for _ in prompts]
+    heads = [len(p) - 4 for p in prompts]
+    model.step(cache, slots, [p[:h] for p, h in zip(prompts, heads)], None)
+    for i in range(4):
+        got = model.step(cache, slots, [[p[h + i]] for p, h in zip(prompts, heads)], "last")
+        for j, (p, ref) in enumerate(zip(prompts, want)):
+            assert rel_err(got[j], ref[heads[j] + i]) < TOL[dtype]
+    # and through the generation loop (eager steps, since the toy mixer decides on the host)
+    res = eng.generate(prompts[:2], 5)
+    assert all(len(r.tokens) == 5 for r in res)
+    model.check_status()
