@@ -152,3 +152,57 @@ extern "C" int fd_sample(const float* logits, int n, int V, const float* tempera
     sample_final_kernel<<<n, 32, 0, stream>>>(part_v, part_i, chunks, out);
     return check_launch("sample_final");
 }
+
+// ---------------------------------------------------------------------------
+// The variant that allocates nothing (declared and described in no_alloc.h).
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Per-chunk winners of the rows of one call: scores first, then indices.  In
+// host code this name is only a handle for cudaGetSymbolAddress; it is not a
+// device pointer and must never be passed to a kernel as one.
+static __device__ __align__(256) unsigned int g_no_alloc_scratch[2 * FD_NO_ALLOC_MAX_ROWS * FD_NO_ALLOC_MAX_CHUNKS];
+
+namespace {
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+void* g_no_alloc_ptr[NO_ALLOC_MAX_DEVICES] = {nullptr};   // device address of the array, per device
+}
+
+extern "C" int fd_sample_no_alloc(const float* logits, int n, int V, const float* temperature,
+                                  const long long* request, const int* step, unsigned long long seed, int* out,
+                                  cudaStream_t stream) {
+    if (n == 0) return 0;
+    FD_REQUIRE(V > 0, -2, "sample_no_alloc: vocabulary %d", V);
+    FD_REQUIRE(n > 0 && n <= FD_NO_ALLOC_MAX_ROWS, -2,
+               "sample_no_alloc: %d rows in one call, the static scratch array holds at most %d", n,
+               FD_NO_ALLOC_MAX_ROWS);
+    const int chunks = (V + SAMPLE_CHUNK - 1) / SAMPLE_CHUNK;
+    FD_REQUIRE(chunks <= FD_NO_ALLOC_MAX_CHUNKS, -2,
+               "sample_no_alloc: a vocabulary of %d needs %d chunks, the static scratch array holds at most %d "
+               "(vocabularies up to %d)", V, chunks, FD_NO_ALLOC_MAX_CHUNKS, FD_NO_ALLOC_MAX_CHUNKS * SAMPLE_CHUNK);
+    FD_REQUIRE(temperature == nullptr || (request != nullptr && step != nullptr), -2,
+               "sample_no_alloc: temperature sampling needs request ids and step counters");
+
+    // set-up, once per device, with that device current: the array's device address
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(-1, "sample_no_alloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    FD_REQUIRE(dev >= 0 && dev < NO_ALLOC_MAX_DEVICES, -2, "sample_no_alloc: device index %d", dev);
+    if (g_no_alloc_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_no_alloc_scratch);
+        if (e != cudaSuccess || ptr == nullptr)
+            return fail(-3, "sample_no_alloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_no_alloc_ptr[dev] = ptr;
+    }
+    float* part_v = static_cast<float*>(g_no_alloc_ptr[dev]);
+    int* part_i = static_cast<int*>(g_no_alloc_ptr[dev]) + (size_t)chunks * n;
+
+    dim3 grid(chunks, n);
+    sample_partial_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, request, step, seed,
+                                                             part_v, part_i, out, chunks);
+    int rc = check_launch("sample_no_alloc");
+    if (rc != 0 || chunks == 1) return rc;
+    sample_final_kernel<<<n, 32, 0, stream>>>(part_v, part_i, chunks, out);
+    return check_launch("sample_no_alloc_final");
+}
