@@ -84,14 +84,28 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 //   q_out[T, n_q d]
 //   pools [num_blocks, n_kv, block_size, d]
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+template <typename TQ, typename TB>
+__device__ __forceinline__ float qkv_value(const TQ* __restrict__ qkv, int n_parts, size_t part_stride, size_t idx,
+                                           const TB* __restrict__ bias, int col) {
+    float v = to_float(qkv[idx]);
+    for (int p = 1; p < n_parts; ++p) v += to_float(qkv[p * part_stride + idx]);
+    if (bias != nullptr) v += to_float(bias[col]);
+    return v;
+}
+
+// TQ: element type of the projection's output (T, or float partial sums of a
+// split-K product: n_parts arrays part_stride apart, added in index order,
+// plus an optional bias of type TB that the product has not added yet).
+template <typename T, typename TQ, typename TB>
+__global__ void rope_append_kernel(const TQ* __restrict__ qkv, int n_parts, size_t part_stride,
+                                   const TB* __restrict__ bias, T* __restrict__ q_out,
                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                    int table_len, const int* __restrict__ tok_row,
                                    const int* __restrict__ tok_pos, const int* __restrict__ row_slot,
                                    T* __restrict__ k_pool, T* __restrict__ v_pool,
                                    const int* __restrict__ block_table, int max_blocks, int num_blocks,
-                                   int block_size, int n_q, int n_kv, int d, int write_kv, int* status) {
+                                   int block_size, int n_q, int n_kv, int d, int write_kv, int paired,
+                                   int* status) {
     const int t = blockIdx.x;
     const int half = d >> 1;
     const int slot = row_slot[tok_row[t]];
@@ -104,7 +118,7 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
     }
     const float* c = cos_t + (size_t)pos * half;
     const float* s = sin_t + (size_t)pos * half;
-    const T* row = qkv + (size_t)t * (n_q + 2 * n_kv) * d;
+    const size_t row = (size_t)t * (n_q + 2 * n_kv) * d;
 
     // destination of this token's keys and values
     T* kdst = nullptr;
@@ -124,8 +138,12 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
     const int n_rot = (n_q + n_kv) * half;
     for (int e = threadIdx.x; e < n_rot; e += blockDim.x) {
         const int h = e / half, j = e - h * half;
-        const float x1 = to_float(row[h * d + j]);
-        const float x2 = to_float(row[h * d + j + half]);
+        // columns of dim j and of its partner j + d/2: natural order, or (paired) tiles of
+        // 16 columns holding dims 8t .. 8t+7 and then d/2 + 8t .. d/2 + 8t+7
+        const int c1 = paired ? h * d + (j >> 3) * 16 + (j & 7) : h * d + j;
+        const int c2 = paired ? c1 + 8 : c1 + half;
+        const float x1 = qkv_value(qkv, n_parts, part_stride, row + c1, bias, c1);
+        const float x2 = qkv_value(qkv, n_parts, part_stride, row + c2, bias, c2);
         const float cj = c[j], sj = s[j];
         const T y1 = from_float<T>(x1 * cj - x2 * sj);
         const T y2 = from_float<T>(x2 * cj + x1 * sj);
@@ -140,11 +158,27 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, T* __restrict__ q_
         }
     }
     if (vdst != nullptr) {
-        const T* vrow = row + (size_t)(n_q + n_kv) * d;
+        const int voff = (n_q + n_kv) * d;
         for (int e = threadIdx.x; e < n_kv * d; e += blockDim.x) {
             const int h = e / d, j = e - h * d;
-            vdst[h * head_stride + j] = vrow[e];
+            vdst[h * head_stride + j] = from_float<T>(qkv_value(qkv, n_parts, part_stride, row + voff + e, bias, voff + e));
         }
+    }
+}
+
+// out[m, i] = silu(g) * u where gate and up values of a row come in tiles of
+// 16 columns: 8 gate values, then the 8 up values of the same outputs.
+template <typename T>
+__global__ void silu_mul_tiled_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; e < total; e += stride) {
+        const size_t m = e / I;
+        const int i = (int)(e - m * I);
+        const size_t base = m * 2 * I + (size_t)(i >> 3) * 16 + (i & 7);
+        const float g = to_float(gu[base]);
+        const float u = to_float(gu[base + 8]);
+        out[e] = from_float<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
@@ -204,37 +238,57 @@ extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, l
     return fail(-2, "add_rmsnorm: unsupported dtypes delta=%d out=%d", delta_dtype, out_dtype);
 }
 
-extern "C" int fd_silu_mul(const void* gu, void* out, int dtype, int M, int I, cudaStream_t stream) {
+// tiled == 0: gu = [gate (I columns) | up (I columns)]; tiled != 0: tiles of 8 gate + 8 up columns.
+extern "C" int fd_silu_mul(const void* gu, void* out, int dtype, int M, int I, int tiled, cudaStream_t stream) {
     const size_t total = (size_t)M * I;
     if (total == 0) return 0;
+    FD_REQUIRE(!tiled || I % 8 == 0, -2, "silu_mul: the tiled layout needs a multiple of 8 outputs, got %d", I);
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (dtype == 0)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
-    else
-        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+    if (dtype == 0) {
+        if (tiled) silu_mul_tiled_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+        else silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    } else {
+        if (tiled) silu_mul_tiled_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+        else silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+    }
     return check_launch("silu_mul");
 }
 
-extern "C" int fd_rope_append(const void* qkv, void* q_out, int dtype, const float* cos_t, const float* sin_t,
-                              int table_len, const int* tok_row, const int* tok_pos, const int* row_slot,
-                              void* k_pool, void* v_pool, const int* block_table, int max_blocks,
-                              int num_blocks, int block_size, int T, int n_q, int n_kv, int d, int write_kv,
-                              int* status, cudaStream_t stream) {
+// qkv_dtype: element type of `qkv` (0 float, 1 bfloat16); with n_parts > 1 it
+// holds float partial sums part_stride elements apart.  bias (dtype bias_dtype)
+// may be null.  dtype: type of q_out and of the cache.  paired != 0: the
+// columns of every q and k head are in tiles of 8 dims + their 8 rotation
+// partners (the row order the decode projection kernel wants of W).
+extern "C" int fd_rope_append(const void* qkv, int qkv_dtype, int n_parts, long long part_stride,
+                              const void* bias, int bias_dtype, void* q_out, int dtype, const float* cos_t,
+                              const float* sin_t, int table_len, const int* tok_row, const int* tok_pos,
+                              const int* row_slot, void* k_pool, void* v_pool, const int* block_table,
+                              int max_blocks, int num_blocks, int block_size, int T, int n_q, int n_kv, int d,
+                              int write_kv, int paired, int* status, cudaStream_t stream) {
     if (T == 0) return 0;
     FD_REQUIRE(d > 0 && d % 2 == 0, -2, "rope_append: head size %d must be even", d);
+    FD_REQUIRE(!paired || d % 16 == 0, -2, "rope_append: the paired column order needs a head size that is a multiple of 16, got %d", d);
     FD_REQUIRE(block_size > 0 && n_q > 0 && n_kv > 0, -2, "rope_append: bad sizes");
+    FD_REQUIRE(n_parts >= 1 && (n_parts == 1 || qkv_dtype == 0), -2, "rope_append: partial sums must be float");
     const int work = (n_q + n_kv) * d / 2;
     const int threads = work >= 512 ? 256 : 128;
-    if (dtype == 0)
-        rope_append_kernel<float><<<T, threads, 0, stream>>>(
-            (const float*)qkv, (float*)q_out, cos_t, sin_t, table_len, tok_row, tok_pos, row_slot,
-            (float*)k_pool, (float*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv, d,
-            write_kv, status);
-    else
-        rope_append_kernel<bf16><<<T, threads, 0, stream>>>(
-            (const bf16*)qkv, (bf16*)q_out, cos_t, sin_t, table_len, tok_row, tok_pos, row_slot,
-            (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv, d,
-            write_kv, status);
+    const size_t ps = (size_t)part_stride;
+#define FD_ROPE_LAUNCH(T_, TQ_, TB_)                                                                          \
+    rope_append_kernel<T_, TQ_, TB_><<<T, threads, 0, stream>>>(                                               \
+        (const TQ_*)qkv, n_parts, ps, (const TB_*)bias, (T_*)q_out, cos_t, sin_t, table_len, tok_row, tok_pos, \
+        row_slot, (T_*)k_pool, (T_*)v_pool, block_table, max_blocks, num_blocks, block_size, n_q, n_kv, d,     \
+        write_kv, paired, status)
+    if (dtype == 0) {
+        FD_REQUIRE(qkv_dtype == 0 && (bias == nullptr || bias_dtype == 0), -2, "rope_append: float32 path takes float32 inputs");
+        FD_ROPE_LAUNCH(float, float, float);
+    } else if (qkv_dtype == 1) {
+        if (bias != nullptr && bias_dtype == 0) FD_ROPE_LAUNCH(bf16, bf16, float);
+        else FD_ROPE_LAUNCH(bf16, bf16, bf16);
+    } else {
+        if (bias != nullptr && bias_dtype == 0) FD_ROPE_LAUNCH(bf16, float, float);
+        else FD_ROPE_LAUNCH(bf16, float, bf16);
+    }
+#undef FD_ROPE_LAUNCH
     return check_launch("rope_append");
 }

@@ -1,0 +1,400 @@
+// Weight-streaming matrix product for decode steps (bfloat16):
+//     out[m, n] = sum_k x[m, k] W[n, k]        M <= 64 rows of x, W [N, K] row-major
+//
+// At M <= 64 the product is bound by reading W once from HBM, so the kernel is
+// built around that stream.  The roles of the operands are swapped for the
+// tensor cores: 16 rows of W are the M side of mma.m16n8k16 and 8 rows of x the
+// N side, so no tensor work is wasted on padding a tiny batch up to a 64- or
+// 128-row tile.  Each thread loads 16 contiguous bytes of its W row straight
+// from global memory into registers (W is never staged in shared memory): with
+// the k index permuted identically on both operands, those 8 values ARE two A
+// fragments, and 16 bytes of an x row (from global memory, which L1/L2 serve)
+// are the matching B fragments.  Several such loads are in flight per thread
+// before the first is used, and nothing waits at the start of the kernel.
+//
+// A CTA has 8 warps arranged as WR row tiles x WK slices of K (WR * WK = 8):
+// wide matrices use WK = 1 (128 rows per CTA), narrow ones WK = 8 (16 rows per
+// CTA, the warps' partial sums added in shared memory in a fixed order), so
+// that N / (16 WR) CTAs cover the GPU without partial sums in global memory.
+// grid.y splits K across CTAs as well.  Outputs:
+//   * mode 0: float partial sums [split, M, N] that a consumer adds up;
+//   * modes 1, 2: out = sum (+ bias) as bfloat16 or float.  With n_splits > 1
+//     the CTAs of one row block form a thread-block cluster; each leaves its
+//     partial tile in its own shared memory and the cluster's first CTA adds
+//     them through distributed shared memory in rank order, so no partial sum
+//     ever goes to global memory;
+//   * gated: W rows come in tiles of 16 = 8 gate rows then 8 up rows, so a
+//     thread holds gate_i and up_i together and writes silu(gate_i) * up_i.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace fd {
+
+constexpr int GV_WARPS = 8;
+constexpr int GV_THREADS = GV_WARPS * 32;
+
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    // weights are read once per step: do not let them displace activations in L1
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+struct GemvParams {
+    const __nv_bfloat16* x;      // [M, K]
+    const __nv_bfloat16* w;      // [N, K]
+    const void* bias;            // [N] or null (bf16 or float, see bias_f32)
+    void* out;                   // see mode
+    int M, N, K;
+    int k_per_split;             // multiple of 32
+    int n_splits;
+    int mode;                    // 0: partial float [split, M, N]; 1: bf16 [M, N]; 2: float [M, N]; 3: gated bf16 [M, N / 2];
+                                 // 4: q/k/v projection with rotary encoding and cache append (see RopeArgs)
+    int bias_f32;
+};
+
+// Mode 4.  W rows are the q heads, then the k heads, then the v heads.  Inside a
+// q or k head the rows come in tiles of 16: dims 8t .. 8t+7 and then their
+// rotation partners d/2 + 8t .. d/2 + 8t+7, so the thread that holds x_j also
+// holds x_{j + d/2}.  v heads are in natural order.  `out` is q_out [M, n_q d].
+struct RopeArgs {
+    const float* cos_t;          // [table_len, d/2]
+    const float* sin_t;
+    const int* tok_row;          // [M]
+    const int* tok_pos;          // [M]
+    const int* row_slot;
+    __nv_bfloat16* k_pool;       // [num_blocks, n_kv, block_size, d]
+    __nv_bfloat16* v_pool;
+    const int* block_table;
+    int* status;
+    int table_len, max_blocks, num_blocks, block_size;
+    int n_q, n_kv, d, write_kv;
+};
+
+template <int NT, int WK, int UNROLL, bool CLUSTER>
+__global__ void __launch_bounds__(GV_THREADS)
+gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
+    constexpr int WR = GV_WARPS / WK;
+    __shared__ float red[WK > 1 ? GV_WARPS * 32 * NT * 4 : 1];
+    __shared__ float ctile[CLUSTER ? WR * 32 * NT * 4 : 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wr = warp / WK, wk = warp % WK;
+    const int split = blockIdx.y;
+    const int k0 = split * p.k_per_split;
+    const int k1 = min(p.K, k0 + p.k_per_split);
+    const int n_chunks = (k1 - k0) >> 5;              // chunks of 32 k in this CTA's range
+
+    const int r = lane >> 2, q = lane & 3;
+    const int row0 = (blockIdx.x * WR + wr) * 16 + r;           // this thread's W rows: row0 and row0 + 8
+    // rows beyond N (and x rows beyond M) read the last valid row; their results are never stored
+    const __nv_bfloat16* w0 = p.w + (size_t)min(row0, p.N - 1) * p.K + k0 + q * 8;
+    const __nv_bfloat16* w1 = p.w + (size_t)min(row0 + 8, p.N - 1) * p.K + k0 + q * 8;
+    const __nv_bfloat16* xb[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) xb[nt] = p.x + (size_t)min(nt * 8 + r, p.M - 1) * p.K + k0 + q * 8;
+
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    // this warp takes chunks wk, wk + WK, ...: at any moment the WK warps of a row tile read
+    // neighbouring 64-byte pieces of the same rows
+    int kc = wk;
+    for (; kc + (UNROLL - 1) * WK < n_chunks; kc += UNROLL * WK) {
+        uint4 a[UNROLL], b[UNROLL], xv[UNROLL][NT];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            a[u] = ldg_stream(w0 + (kc + u * WK) * 32);
+            b[u] = ldg_stream(w1 + (kc + u * WK) * 32);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+                xv[u][nt] = __ldg(reinterpret_cast<const uint4*>(xb[nt] + (kc + u * WK) * 32));
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                mma16816(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, xv[u][nt].x, xv[u][nt].y);
+                mma16816(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, xv[u][nt].z, xv[u][nt].w);
+            }
+        }
+    }
+    for (; kc < n_chunks; kc += WK) {
+        const uint4 a = ldg_stream(w0 + kc * 32);
+        const uint4 b = ldg_stream(w1 + kc * 32);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint4 xv = __ldg(reinterpret_cast<const uint4*>(xb[nt] + kc * 32));
+            mma16816(acc[nt], a.x, b.x, a.y, b.y, xv.x, xv.y);
+            mma16816(acc[nt], a.z, b.z, a.w, b.w, xv.z, xv.w);
+        }
+    }
+
+    if (WK > 1) {
+        // add the K slices of a row tile in the order wk = 0, 1, ...
+        float* mine = red + (warp * 32 + lane) * NT * 4;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) mine[nt * 4 + e] = acc[nt][e];
+        __syncthreads();
+        if (wk == 0) {
+#pragma unroll
+            for (int k = 1; k < WK; ++k) {
+                const float* other = red + ((warp + k) * 32 + lane) * NT * 4;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[nt][e] += other[nt * 4 + e];
+            }
+        }
+    }
+    if (CLUSTER) {
+        // the CTAs of a cluster hold the K splits of the same rows: rank 0 adds the others'
+        // tiles out of their shared memory, in rank order
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        float* tile = ctile + (wr * 32 + lane) * NT * 4;
+        if (wk == 0 && cluster.block_rank() != 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) tile[nt * 4 + e] = acc[nt][e];
+        }
+        cluster.sync();
+        if (wk == 0 && cluster.block_rank() == 0) {
+            const int n = cluster.num_blocks();
+            for (int rk = 1; rk < n; ++rk) {
+                const float* remote = cluster.map_shared_rank(tile, rk);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[nt][e] += remote[nt * 4 + e];
+            }
+        }
+        cluster.sync();                          // the others' shared memory stays alive until it has been read
+        if (cluster.block_rank() != 0) return;
+    }
+    if (WK > 1 && wk != 0) return;
+
+    // epilogue: acc[nt][0..1] -> W row row0, x rows nt*8 + q*2 + {0,1}; acc[nt][2..3] -> W row row0 + 8
+    if (p.mode == 4) {
+        const int d = ra.d, half = d >> 1, tiles_per_head = d >> 4;
+        const int tile = row0 >> 4;
+        const int head = tile / tiles_per_head, t_in = tile - head * tiles_per_head;
+        if (head >= ra.n_q + 2 * ra.n_kv) return;
+        float b0 = 0.f, b1 = 0.f;
+        if (p.bias != nullptr) {
+            b0 = p.bias_f32 ? static_cast<const float*>(p.bias)[row0] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row0]);
+            b1 = p.bias_f32 ? static_cast<const float*>(p.bias)[row0 + 8] : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[row0 + 8]);
+        }
+        const bool is_v = head >= ra.n_q + ra.n_kv;
+        // dims of this thread's two values inside the head
+        const int j0 = is_v ? t_in * 16 + r : t_in * 8 + r;
+        const int j1 = is_v ? j0 + 8 : j0 + half;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int m = nt * 8 + q * 2 + e;
+                if (m >= p.M) continue;
+                const int slot = ra.row_slot[ra.tok_row[m]];
+                if (slot < 0) continue;                       // padding row
+                float v0 = acc[nt][e] + b0, v1 = acc[nt][2 + e] + b1;
+                int pos = ra.tok_pos[m];
+                const bool pos_ok = pos >= 0 && pos < ra.table_len;
+                if (!pos_ok) { set_status(ra.status, STATUS_BAD_POSITION); pos = 0; }
+                if (!is_v) {
+                    const float c = ra.cos_t[(size_t)pos * half + j0], sn = ra.sin_t[(size_t)pos * half + j0];
+                    const float y0 = v0 * c - v1 * sn, y1 = v1 * c + v0 * sn;
+                    v0 = y0; v1 = y1;
+                }
+                if (head < ra.n_q) {
+                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + ((size_t)m * ra.n_q + head) * d;
+                    o[j0] = __float2bfloat16_rn(v0);
+                    o[j1] = __float2bfloat16_rn(v1);
+                } else if (ra.write_kv && pos_ok) {
+                    const int blk = ra.block_table[(size_t)slot * ra.max_blocks + pos / ra.block_size];
+                    if (blk < 0 || blk >= ra.num_blocks) { set_status(ra.status, STATUS_BAD_BLOCK); continue; }
+                    const int kvh = is_v ? head - ra.n_q - ra.n_kv : head - ra.n_q;
+                    __nv_bfloat16* pool = is_v ? ra.v_pool : ra.k_pool;
+                    __nv_bfloat16* o = pool + (((size_t)blk * ra.n_kv + kvh) * ra.block_size + pos % ra.block_size) * d;
+                    o[j0] = __float2bfloat16_rn(v0);
+                    o[j1] = __float2bfloat16_rn(v1);
+                }
+            }
+        return;
+    }
+    if (p.mode == 3) {
+        // tiles of 16 rows hold 8 gate rows then 8 up rows of the same 8 outputs
+        const int tile = row0 >> 4;
+        const int o = tile * 8 + r;                   // output feature
+        const int NO = p.N >> 1;
+        if (o < NO) {
+            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int m = nt * 8 + q * 2 + e;
+                    if (m < p.M) {
+                        const float g = acc[nt][e], u = acc[nt][2 + e];
+                        out[(size_t)m * NO + o] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+                    }
+                }
+        }
+        return;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int n = row0 + h * 8;
+        if (n >= p.N) continue;
+        float bias = 0.f;
+        if (p.bias != nullptr && p.mode != 0)
+            bias = p.bias_f32 ? static_cast<const float*>(p.bias)[n]
+                              : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int m = nt * 8 + q * 2 + e;
+                if (m >= p.M) continue;
+                const float v = acc[nt][h * 2 + e] + bias;
+                if (p.mode == 0)
+                    static_cast<float*>(p.out)[((size_t)split * p.M + m) * p.N + n] = v;
+                else if (p.mode == 1)
+                    static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.N + n] = __float2bfloat16_rn(v);
+                else
+                    static_cast<float*>(p.out)[(size_t)m * p.N + n] = v;
+            }
+    }
+}
+
+template <int NT, int WK, int UNROLL>
+static int launch_gemv(const GemvParams& p, const RopeArgs& ra, cudaStream_t stream) {
+    constexpr int rows = 16 * (GV_WARPS / WK);
+    dim3 grid((p.N + rows - 1) / rows, p.n_splits);
+    if (p.n_splits > 1 && p.mode != 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(GV_THREADS);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = p.n_splits;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<NT, WK, UNROLL, true>, p, ra);
+        if (e != cudaSuccess) return fail(-100, "gemv_mma: cluster launch failed: %s", cudaGetErrorString(e));
+        return 0;
+    }
+    gemv_mma_kernel<NT, WK, UNROLL, false><<<grid, GV_THREADS, 0, stream>>>(p, ra);
+    return check_launch("gemv_mma");
+}
+
+// Measured on B200 (graph-timed, weights beyond L2): wide matrices stream best with 32 rows
+// per CTA (4 or more CTAs per SM), narrow ones with 16 rows per CTA plus a split of K.
+static int pick_wk(int N) { return N >= 8192 ? 4 : 8; }
+
+template <int NT, int UNROLL>
+static int launch_gemv_wk(const GemvParams& p, const RopeArgs& ra, cudaStream_t stream) {
+    if (pick_wk(p.N) == 4) return launch_gemv<NT, 4, UNROLL>(p, ra, stream);
+    return launch_gemv<NT, 8, UNROLL>(p, ra, stream);
+}
+
+static int run_gemv(GemvParams& p, const RopeArgs& ra, cudaStream_t stream) {
+    const int chunks = p.K / 32;
+    p.k_per_split = ((chunks + p.n_splits - 1) / p.n_splits) * 32;
+    FD_REQUIRE((long long)p.k_per_split * (p.n_splits - 1) < p.K, -2, "gemv: %d splits leave one empty for K=%d", p.n_splits, p.K);
+    const int nt = p.M <= 8 ? 1 : (p.M <= 16 ? 2 : (p.M <= 32 ? 4 : 8));
+    switch (nt) {
+        case 1: return launch_gemv_wk<1, 8>(p, ra, stream);
+        case 2: return launch_gemv_wk<2, 4>(p, ra, stream);
+        case 4: return launch_gemv_wk<4, 2>(p, ra, stream);
+        default: return launch_gemv_wk<8, 1>(p, ra, stream);
+    }
+}
+
+}  // namespace fd
+
+using namespace fd;
+
+// How many splits of K (each a multiple of 32 wide, as CTAs of their own) the
+// product would use to reach about `target_ctas` CTAs; 1 when the rows alone
+// give enough.  0: sizes not taken (M > 64, K not a multiple of 32): use another
+// matrix product.
+extern "C" int fd_gemv_splits(int M, int N, int K, int target_ctas, int allow_split) {
+    if (M < 1 || M > 64 || K < 32 || K % 32 != 0 || N < 1) return 0;
+    if (!allow_split) return 1;
+    const int rows = 16 * (GV_WARPS / pick_wk(N));
+    const int row_blocks = (N + rows - 1) / rows;
+    int want = (target_ctas + row_blocks / 2) / row_blocks;
+    const int chunks = K / 32;
+    if (want > chunks / 8) want = chunks / 8;             // a split keeps at least 8 chunks (256 k)
+    if (want > 8) want = 8;                               // the most CTAs a portable cluster holds
+    if (want < 1) want = 1;
+    const int per = ((chunks + want - 1) / want) * 32;    // k per split, multiple of 32
+    return (K + per - 1) / per;
+}
+
+// mode 0: out = float partial sums [n_splits, M, N]; 1: bf16 [M, N]; 2: float [M, N] (both with
+// up to 8 splits added inside a cluster); 3: gated (rows of W in tiles of 8 gate + 8 up):
+// bf16 [M, N / 2], n_splits == 1.
+extern "C" int fd_gemv(const void* x, const void* w, const void* bias, int bias_f32, void* out, int mode,
+                       int M, int N, int K, int n_splits, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    FD_REQUIRE(M >= 1 && M <= 64, -2, "gemv: %d rows of x; this kernel takes 1..64", M);
+    FD_REQUIRE(K >= 32 && K % 32 == 0, -2, "gemv: K=%d must be a positive multiple of 32", K);
+    FD_REQUIRE(n_splits >= 1 && (mode != 3 || n_splits == 1), -2, "gemv: the gated form cannot be split over K");
+    FD_REQUIRE(mode == 0 || n_splits <= 8, -2, "gemv: at most 8 splits add up inside a cluster, got %d", n_splits);
+    FD_REQUIRE(mode >= 0 && mode <= 3, -2, "gemv: mode %d", mode);
+    FD_REQUIRE(mode != 3 || N % 16 == 0, -2, "gemv: gated output needs N (= 2 x outputs) to be a multiple of 16, got %d", N);
+    FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, -2, "gemv: x and W must be 16-byte aligned");
+    GemvParams p;
+    p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = out;
+    p.M = M; p.N = N; p.K = K; p.n_splits = n_splits; p.mode = mode; p.bias_f32 = bias_f32;
+    RopeArgs ra = {};
+    return run_gemv(p, ra, stream);
+}
+
+// The q/k/v projection of a decode step with its epilogue: bias, rotary
+// encoding of q and k (float), q to q_out [M, n_q d], k and v into the paged
+// cache at each token's position.  W [(n_q + 2 n_kv) d, K] and bias must have
+// the rows of every q and k head in tiles of 8 dims + their 8 partners (see
+// RopeArgs).  Up to 8 splits of K add up inside a cluster.
+extern "C" int fd_gemv_qkv_rope(const void* x, const void* w, const void* bias, int bias_f32, void* q_out,
+                                int M, int K, int n_splits, const float* cos_t, const float* sin_t, int table_len,
+                                const int* tok_row, const int* tok_pos, const int* row_slot, void* k_pool,
+                                void* v_pool, const int* block_table, int max_blocks, int num_blocks,
+                                int block_size, int n_q, int n_kv, int d, int write_kv, int* status,
+                                cudaStream_t stream) {
+    if (M == 0) return 0;
+    FD_REQUIRE(M >= 1 && M <= 64, -2, "gemv: %d rows of x; this kernel takes 1..64", M);
+    FD_REQUIRE(K >= 32 && K % 32 == 0, -2, "gemv: K=%d must be a positive multiple of 32", K);
+    FD_REQUIRE(d >= 16 && d % 16 == 0, -2, "gemv_qkv_rope: head size %d must be a multiple of 16", d);
+    FD_REQUIRE(n_splits >= 1 && n_splits <= 8, -2, "gemv: at most 8 splits add up inside a cluster, got %d", n_splits);
+    FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0, -2, "gemv: x and W must be 16-byte aligned");
+    GemvParams p;
+    p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = q_out;
+    p.M = M; p.N = (n_q + 2 * n_kv) * d; p.K = K; p.n_splits = n_splits; p.mode = 4; p.bias_f32 = bias_f32;
+    RopeArgs ra;
+    ra.cos_t = cos_t; ra.sin_t = sin_t; ra.tok_row = tok_row; ra.tok_pos = tok_pos; ra.row_slot = row_slot;
+    ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool; ra.block_table = block_table;
+    ra.status = status; ra.table_len = table_len; ra.max_blocks = max_blocks; ra.num_blocks = num_blocks;
+    ra.block_size = block_size; ra.n_q = n_q; ra.n_kv = n_kv; ra.d = d; ra.write_kv = write_kv;
+    return run_gemv(p, ra, stream);
+}

@@ -368,7 +368,8 @@ class Model:
         for i, run in enumerate(self.schedule):
             delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[i])
             if self.trace is not None:
-                self.trace[f"layer.{i}"] = (resid + delta.float()).cpu()
+                d = delta.float().sum(0) if delta.dim() == 3 else delta.float()
+                self.trace[f"layer.{i}"] = (resid + d).cpu()
         if ctx.n_want == 0:
             return None
         xn = ctx.ws.get("final_normed", (ctx.n_want, self.hidden_size), self.dtype)

@@ -72,8 +72,11 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_sm_count": [],
         "fd_embed": [P, P, I, P, I, I, I, P, P],
         "fd_add_rmsnorm": [P, I, I, LL, P, I, P, I, F, P, I, P, I, I, P],
-        "fd_silu_mul": [P, P, I, I, I, P],
-        "fd_rope_append": [P, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P],
+        "fd_silu_mul": [P, P, I, I, I, I, P],
+        "fd_rope_append": [P, I, I, LL, P, I, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
+        "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+        "fd_gemv_splits": [I, I, I, I, I],
+        "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P],
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
         "fd_attn_simt_qt": [I],
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
@@ -147,8 +150,10 @@ def add_rmsnorm(delta: Optional[torch.Tensor], resid: torch.Tensor, weight: torc
                 write_resid: bool = True, n_parts: int = 1) -> None:
     """out[j] = rmsnorm(resid[r] + delta[r]) * weight with r = rows[j] (or j);
     resid[r] takes the sum when ``write_resid``.  ``delta`` None: plain norm.
-    ``delta`` with ``n_parts`` > 1 is [n_parts, rows, H], summed in order."""
+    ``delta`` [parts, rows, H] (or ``n_parts`` > 1) holds partial sums, added in order."""
     H = resid.shape[-1]
+    if delta is not None and delta.dim() == 3:
+        n_parts = delta.shape[0]
     if n_out is None:
         n_out = rows.numel() if rows is not None else resid.numel() // H
     assert resid.dtype == torch.float32 and out.shape[-1] == H and weight.numel() == H
@@ -161,28 +166,80 @@ def add_rmsnorm(delta: Optional[torch.Tensor], resid: torch.Tensor, weight: torc
                                 n_out, H, _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, tiled: bool = False) -> None:
+    """out[m, i] = silu(gate_i) * up_i.  ``gate_up`` [M, 2I] is [gate | up], or
+    with ``tiled`` tiles of 16 columns: 8 gate values then the 8 up values."""
     M, I2 = gate_up.shape
     assert out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
-    _check(lib().fd_silu_mul(_ptr(gate_up), _ptr(out), _dt(out.dtype), M, I2 // 2, _stream()))
+    _check(lib().fd_silu_mul(_ptr(gate_up), _ptr(out), _dt(out.dtype), M, I2 // 2, int(tiled), _stream()))
 
 
 def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
                 tok_row: torch.Tensor, tok_pos: torch.Tensor, row_slot: torch.Tensor,
                 k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
-                n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor) -> None:
+                n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, paired: bool = False) -> None:
     """Rotate q and k of every token at its position; append k and v to the
-    paged pools [num_blocks, n_kv, block_size, d] (unless ``write_kv`` is off)."""
-    T = qkv.shape[0]
-    assert qkv.shape[1] == (n_q + 2 * n_kv) * head_dim and q_out.shape == (T, n_q * head_dim)
+    paged pools [num_blocks, n_kv, block_size, d] (unless ``write_kv`` is off).
+    ``qkv`` is [T, (n_q + 2 n_kv) d], or [parts, T, ...] float32 partial sums of
+    a split-K product that are added up here, with ``bias`` added on top.
+    ``paired``: the columns of each q and k head come in tiles of 8 dims + their
+    8 rotation partners (the order ``gemv_qkv_rope`` wants the rows of W in)."""
+    n_parts = qkv.shape[0] if qkv.dim() == 3 else 1
+    T = qkv.shape[-2]
+    assert qkv.shape[-1] == (n_q + 2 * n_kv) * head_dim and q_out.shape == (T, n_q * head_dim)
     assert cos.dtype == torch.float32 and cos.shape[1] == head_dim // 2
-    assert k_pool.dtype == qkv.dtype and q_out.dtype == qkv.dtype
+    assert k_pool.dtype == q_out.dtype and (n_parts == 1 or qkv.dtype == torch.float32)
     num_blocks, _, block_size, _ = k_pool.shape
-    _check(lib().fd_rope_append(_ptr(qkv), _ptr(q_out), _dt(qkv.dtype), _ptr(cos), _ptr(sin), cos.shape[0],
-                                _ptr(tok_row), _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool),
-                                _ptr(block_table), block_table.shape[1], num_blocks, block_size, T, n_q, n_kv,
-                                head_dim, int(write_kv), _ptr(status), _stream()))
+    _check(lib().fd_rope_append(_ptr(qkv), _dt(qkv.dtype), n_parts, qkv.numel() // n_parts, _ptr(bias),
+                                _dt(bias.dtype) if bias is not None else 0, _ptr(q_out), _dt(q_out.dtype),
+                                _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_row), _ptr(tok_pos), _ptr(row_slot),
+                                _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], num_blocks,
+                                block_size, T, n_q, n_kv, head_dim, int(write_kv), int(paired), _ptr(status),
+                                _stream()))
+
+
+def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                  cos: torch.Tensor, sin: torch.Tensor, tok_row: torch.Tensor, tok_pos: torch.Tensor,
+                  row_slot: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                  n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor, n_splits: int = 1) -> None:
+    """The q/k/v projection of a decode step (M <= 64 rows, bfloat16) with bias,
+    rotary encoding and the append to the paged cache in its epilogue.  ``w``
+    and ``bias`` are in the paired row order (see ``rope_append``)."""
+    M, K = x.shape
+    assert w.shape == ((n_q + 2 * n_kv) * head_dim, K) and q_out.shape == (M, n_q * head_dim)
+    assert x.dtype == w.dtype == q_out.dtype == k_pool.dtype == torch.bfloat16
+    num_blocks, _, block_size, _ = k_pool.shape
+    _check(lib().fd_gemv_qkv_rope(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                                  _ptr(q_out), M, K, n_splits, _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_row),
+                                  _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                  block_table.shape[1], num_blocks, block_size, n_q, n_kv, head_dim, int(write_kv),
+                                  _ptr(status), _stream()))
+
+
+GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
+
+
+def gemv_splits(M: int, N: int, K: int, target_ctas: int, allow_split: bool = True) -> int:
+    """Splits of K the decode matrix product would use; 0 if it does not take the sizes."""
+    return int(lib().fd_gemv_splits(M, N, K, target_ctas, int(allow_split)))
+
+
+def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
+         n_splits: int = 1) -> None:
+    """Weight-streaming product for M <= 64 rows (bfloat16): out = x w^T.
+    mode GEMV_PARTIAL: out float32 [n_splits, M, N]; GEMV_BF16 / GEMV_F32: out
+    [M, N] (+ bias), with ``n_splits`` <= 8 splits of K added inside a
+    thread-block cluster; GEMV_GATED: w rows in tiles of 8 gate + 8 up, out
+    bfloat16 [M, N / 2] = silu(gate) * up."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
+    want = {GEMV_PARTIAL: (torch.float32, n_splits * M * N), GEMV_BF16: (torch.bfloat16, M * N),
+            GEMV_F32: (torch.float32, M * N), GEMV_GATED: (torch.bfloat16, M * N // 2)}[mode]
+    assert out.dtype == want[0] and out.numel() == want[1], (out.dtype, out.shape, mode)
+    _check(lib().fd_gemv(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                         _ptr(out), mode, M, N, K, n_splits, _stream()))
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:

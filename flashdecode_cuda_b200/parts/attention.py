@@ -11,7 +11,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import KVRequest, LayerCache, Mixer, Runtime
-from .linear import matmul
+from .linear import GEMV_MAX_ROWS, matmul
 
 
 def plan_splits(n_rows: int, n_kv: int, kv_len_bound: int, sm_count: int):
@@ -64,16 +64,34 @@ class GQAAttention(Mixer):
     def kv_request(self) -> KVRequest:
         return KVRequest(self.n_kv, self.d, self.window)
 
+    def _paired_order(self) -> torch.Tensor:
+        """Row order of the packed q/k/v matrix: inside every q and k head, tiles
+        of 8 dims followed by their 8 rotation partners (dims + d/2), so that the
+        decode kernel's thread that holds x_j also holds x_{j + d/2}
+        (csrc/gemv_mma.cu, mode 4); v heads stay in natural order."""
+        d, half = self.d, self.d // 2
+        head = torch.arange(d).view(2, d // 16, 8).permute(1, 0, 2).reshape(d)     # [t][lo|hi][8] -> dims
+        rows = [h * d + head for h in range(self.n_q + self.n_kv)]
+        rows += [torch.arange((self.n_q + self.n_kv) * d, (self.n_q + 2 * self.n_kv) * d)]
+        return torch.cat(rows)
+
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         p = self.prefix
         names = [f"{p}.{x}_proj" for x in "qkv"]
         # one [ (n_q + 2 n_kv) d, H ] matrix: one product instead of three
-        self.w_qkv = torch.cat([tensors.pop(f"{n}.weight") for n in names], dim=0).contiguous()
+        w_qkv = torch.cat([tensors.pop(f"{n}.weight") for n in names], dim=0)
         have = [f"{n}.bias" in tensors for n in names]
         if any(have) and not all(have):
             raise ValueError(f"{p}: q/k/v biases must be all present or all absent")
-        self.b_qkv = torch.cat([tensors.pop(f"{n}.bias") for n in names]).contiguous() if all(have) else None
+        b_qkv = torch.cat([tensors.pop(f"{n}.bias") for n in names]) if all(have) else None
+        self.paired = self.d % 16 == 0
+        if self.paired:
+            order = self._paired_order().to(w_qkv.device)
+            w_qkv = w_qkv[order]
+            b_qkv = b_qkv[order] if b_qkv is not None else None
+        self.w_qkv = w_qkv.contiguous()
+        self.b_qkv = b_qkv.contiguous() if b_qkv is not None else None
         self.w_o = tensors[f"{p}.o_proj.weight"]
 
     def weight_bytes(self) -> int:
@@ -86,11 +104,21 @@ class GQAAttention(Mixer):
     def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
         T, d = ctx.T, self.d
         ws = ctx.ws
-        qkv = ws.get("qkv", (T, (self.n_q + 2 * self.n_kv) * d), x.dtype)
-        matmul(x, self.w_qkv, self.b_qkv, qkv)
         q = ws.get("q_rot", (T, self.n_q * d), x.dtype)
-        K.rope_append(qkv, q, self.position.cos, self.position.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
-                      lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status)
+        rope = self.position
+        splits = 0
+        if self.paired and x.dtype == torch.bfloat16 and T <= GEMV_MAX_ROWS:
+            splits = K.gemv_splits(T, self.w_qkv.shape[0], self.hidden_size, 4 * self.rt.sm_count)
+        if splits >= 1:
+            # decode: projection, bias, rotation and cache append in one kernel
+            K.gemv_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
+                            lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status,
+                            splits)
+        else:
+            qkv = ws.get("qkv", (T, (self.n_q + 2 * self.n_kv) * d), x.dtype)
+            matmul(x, self.w_qkv, self.b_qkv, qkv)
+            K.rope_append(qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool, lc.v_pool,
+                          lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status, paired=self.paired)
         attn = ws.get("attn", (T, self.n_q * d), x.dtype)
         n_splits, split_len, scratch = 1, 0, None
         if ctx.max_q_len == 1:
@@ -103,5 +131,4 @@ class GQAAttention(Mixer):
                          self.n_q, self.n_kv, d, self.scale, self.window or 0, n_splits, split_len, scratch,
                          self.rt.status)
         out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
-        matmul(attn, self.w_o, None, out)
-        return out
+        return matmul(attn, self.w_o, None, out, target_ctas=4 * self.rt.sm_count)

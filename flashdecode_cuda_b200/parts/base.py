@@ -20,7 +20,9 @@ Kinds and their ``forward``:
 
 ``resid`` is the float32 residual stream of the step; ``delta`` the output of
 the previous sub-layer that has not been added to it yet (the deferred add of
-engine/model.py:1-45 in davidjoyme/flashdecode-cuda).
+engine/model.py:1-45 in davidjoyme/flashdecode-cuda).  A ``delta`` is [T, H]
+in the activation dtype, or [parts, T, H] float32 partial sums (a matrix
+product split over K) that the norm adds up in order while it adds the rest.
 """
 
 from __future__ import annotations

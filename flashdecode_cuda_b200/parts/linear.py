@@ -1,10 +1,10 @@
 """Matrix products of the parts: ``out = x w^T (+ bias)`` with ``w [N, K]``.
 
 float32: the library's own FFMA kernel with a fixed summation order (no
-tensor cores, no reduced-precision mode).  bfloat16: the hand-written
-tensor-core kernels where they take the shape, else cuBLAS through torch,
-which is what ``F.linear`` is in davidjoyme/flashdecode-cuda
-(engine/model.py:188-190,208,213-216,232).
+tensor cores, no reduced-precision mode).  bfloat16 with at most 64 rows of x
+(decode steps): the hand-written weight-streaming kernel (``csrc/gemv_mma.cu``).
+Other bfloat16 products: cuBLAS through torch, which is what ``F.linear`` is in
+davidjoyme/flashdecode-cuda (engine/model.py:188-190,208,213-216,232).
 """
 
 from __future__ import annotations
@@ -16,12 +16,25 @@ import torch
 from .. import kernels as K
 
 
-def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+# Up to this many rows the weight-streaming kernel beats the library product (measured on
+# B200 at the sizes of Qwen2.5-1.5B); above it the rows of x no longer fit the registers' reach.
+GEMV_MAX_ROWS = 16
+
+
+def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+           target_ctas: int = 0) -> torch.Tensor:
     """x [M, K], w [N, K], bias [N] or None, out [M, N] (dtype of x, or
-    float32 for logits)."""
+    float32 for logits).  ``target_ctas``: how many CTAs a decode product
+    should spread over (it splits K inside thread-block clusters to get there)."""
     if x.dtype == torch.float32:
         K.gemm_simt(x, w, bias, out)
         return out
+    M, Kd = x.shape
+    if M <= GEMV_MAX_ROWS:
+        splits = K.gemv_splits(M, w.shape[0], Kd, target_ctas, allow_split=target_ctas > 0)
+        if splits >= 1:
+            K.gemv(x, w, bias, out, K.GEMV_F32 if out.dtype == torch.float32 else K.GEMV_BF16, splits)
+            return out
     if out.dtype == torch.float32:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         if bias is not None:

@@ -10,7 +10,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import FeedForward, Runtime
-from .linear import matmul
+from .linear import GEMV_MAX_ROWS, matmul
 
 
 @register_part("feed_forward", "swiglu")
@@ -30,9 +30,17 @@ class SwiGLU(FeedForward):
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
-        p = self.prefix
-        self.w_gate_up = torch.cat([tensors.pop(f"{p}.gate_proj.weight"),
-                                    tensors.pop(f"{p}.up_proj.weight")], dim=0).contiguous()
+        p, I = self.prefix, self.inter
+        gate, up = tensors.pop(f"{p}.gate_proj.weight"), tensors.pop(f"{p}.up_proj.weight")
+        # tiles of 16 rows: 8 gate rows, then the 8 up rows of the same outputs, so the decode
+        # kernel's thread that holds gate_i also holds up_i (csrc/gemv_mma.cu)
+        self.tiled = I % 8 == 0
+        if self.tiled:
+            H = gate.shape[1]
+            self.w_gate_up = torch.stack([gate.view(I // 8, 8, H), up.view(I // 8, 8, H)], dim=1) \
+                .reshape(2 * I, H).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors[f"{p}.down_proj.weight"]
 
     def weight_bytes(self) -> int:
@@ -40,10 +48,13 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         T, ws = ctx.T, ctx.ws
-        gu = ws.get("gate_up", (T, 2 * self.inter), x.dtype)
-        matmul(x, self.w_gate_up, None, gu)
         act = ws.get("ffn_act", (T, self.inter), x.dtype)
-        K.silu_mul(gu, act)
+        if (self.tiled and x.dtype == torch.bfloat16 and T <= GEMV_MAX_ROWS
+                and K.gemv_splits(T, 2 * self.inter, self.hidden_size, 1, allow_split=False) == 1):
+            K.gemv(x, self.w_gate_up, None, act, K.GEMV_GATED)          # product and silu(gate) * up in one kernel
+        else:
+            gu = ws.get("gate_up", (T, 2 * self.inter), x.dtype)
+            matmul(x, self.w_gate_up, None, gu)
+            K.silu_mul(gu, act, tiled=self.tiled)
         out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
-        matmul(act, self.w_down, None, out)
-        return out
+        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count)

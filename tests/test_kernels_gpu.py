@@ -101,6 +101,10 @@ def test_silu_mul(dtype, M, I):
     K.silu_mul(gu, out)
     want = P.swiglu(gu[:, :I].double(), gu[:, I:].double())
     assert rel(out, want) < (1e-6 if dtype == "float32" else 5e-3)
+    if I % 8 == 0:                              # tiles of 8 gate + 8 up columns
+        tiled = torch.stack([gu[:, :I].reshape(M, I // 8, 8), gu[:, I:].reshape(M, I // 8, 8)], dim=2).reshape(M, 2 * I)
+        K.silu_mul(tiled.contiguous(), out, tiled=True)
+        assert rel(out, want) < (1e-6 if dtype == "float32" else 5e-3)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -120,6 +124,58 @@ def test_gemm_simt(dtype, M, N, K_, bias):
         out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
         K.gemm_simt(x, w, b, out32)
         assert rel(out32, want) < 2e-6
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 33, 64])
+@pytest.mark.parametrize("N,K_", [(16, 32), (100, 96), (333, 1536), (2048, 224), (1536, 8960)])
+def test_gemv_decode_product(M, N, K_):
+    """The weight-streaming product of decode steps: every output form, rows of
+    W and of x that fill no tile, K cut into partial sums."""
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    want = P.linear(x.double(), w.double())
+    assert K.gemv_splits(M, N, K_, 1, allow_split=False) in (0, 1)
+    if K.gemv_splits(M, N, K_, 1, allow_split=False) == 1:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        K.gemv(x, w, b, out, K.GEMV_BF16)
+        assert rel(out, want + b.double()) < 5e-3
+        out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        K.gemv(x, w, None, out32, K.GEMV_F32)
+        assert rel(out32, want) < 2e-5
+        K.gemv(x, w, b.float(), out32, K.GEMV_F32)            # a bias kept in 32-bit
+        assert rel(out32, want + b.double()) < 2e-5
+    for target in (1, 64, 296):
+        splits = K.gemv_splits(M, N, K_, target)
+        assert 1 <= splits <= K_ // 32
+        parts = torch.full((splits, M, N), float("nan"), device=DEV)
+        K.gemv(x, w, None, parts, K.GEMV_PARTIAL, splits)
+        assert rel(parts.double().sum(0), want) < 2e-5
+        # the same splits added inside a thread-block cluster: the finished product comes out
+        assert splits <= 8
+        out32 = torch.full((M, N), float("nan"), device=DEV)
+        K.gemv(x, w, b, out32, K.GEMV_F32, splits)
+        assert rel(out32, want + b.double()) < 2e-5
+        out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        K.gemv(x, w, None, out16, K.GEMV_BF16, splits)
+        assert rel(out16, want) < 5e-3
+    if N % 16 == 0 and K.gemv_splits(M, N, K_, 1, allow_split=False) == 1:
+        # gated form: rows in tiles of 8 gate + 8 up
+        I = N // 2
+        gate, up = w[:I], w[I:]
+        tiled = torch.stack([gate.view(I // 8, 8, K_), up.view(I // 8, 8, K_)], dim=1).reshape(N, K_).contiguous()
+        act = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+        K.gemv(x, tiled, None, act, K.GEMV_GATED)
+        assert rel(act, P.swiglu(P.linear(x.double(), gate.double()), P.linear(x.double(), up.double()))) < 6e-3
+
+
+def test_gemv_refuses_what_it_cannot_do():
+    assert K.gemv_splits(65, 128, 64, 1) == 0 and K.gemv_splits(4, 128, 80, 1) == 0
+    x = torch.zeros(4, 80, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(K.KernelError, match="multiple of 32"):
+        K.gemv(x, torch.zeros(16, 80, dtype=torch.bfloat16, device=DEV), None,
+               torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV), K.GEMV_BF16)
 
 
 def test_gemm_simt_rows_do_not_depend_on_the_batch():
@@ -206,6 +262,22 @@ def test_rope_append(dtype, n_q, n_kv, d, bs):
         b = int(table[s, pos // bs])
         assert rel(kp[b, :, pos % bs], rot[t, n_q:]) < tol
         assert torch.equal(vp[b, :, pos % bs].cpu(), qkv.view(T, n_q + 2 * n_kv, d)[t, n_q + n_kv:])
+    # the projection given as float partial sums of a split product, bias still to add
+    g2 = torch.Generator().manual_seed(60)
+    bias = torch.randn((n_q + 2 * n_kv) * d, generator=g2).to(dt)
+    parts = torch.randn(3, T, (n_q + 2 * n_kv) * d, generator=g2)
+    kp2, vp2, q2 = torch.zeros_like(kp), torch.zeros_like(vp), torch.empty_like(q_out)
+    K.rope_append(parts.to(DEV), q2, cos, sin, tok_row.to(DEV), tok_pos.to(DEV),
+                  torch.tensor(slots, dtype=torch.int32, device=DEV), kp2, vp2, table.to(DEV),
+                  n_q, n_kv, d, True, st, bias=bias.to(DEV))
+    x2 = (parts.double().sum(0) + bias.double()).view(T, n_q + 2 * n_kv, d)
+    rot2 = P.apply_rope(x2[:, :n_q + n_kv], c2[tok_pos.long()], s2[tok_pos.long()])
+    assert rel(q2.view(T, n_q, d), rot2[:, :n_q]) < tol
+    t_last = T - 1
+    s_, pos_ = slots[int(tok_row[t_last])], int(tok_pos[t_last])
+    b_ = int(table[s_, pos_ // bs])
+    assert rel(kp2[b_, :, pos_ % bs], rot2[t_last, n_q:]) < tol
+    assert rel(vp2[b_, :, pos_ % bs], x2[t_last, n_q + n_kv:]) < tol
     # nothing else in the pools was touched
     written = sum(new) * n_kv * d
     assert int((kp != 0).sum().item()) <= written
@@ -215,6 +287,76 @@ def test_rope_append(dtype, n_q, n_kv, d, bs):
                   torch.tensor([-1, -1, -1], dtype=torch.int32, device=DEV), kp, vp, table.to(DEV),
                   n_q, n_kv, d, True, st)
     assert int(st.item()) == 0 and float(kp.abs().max()) == 0.0
+
+
+def paired_order(n_q, n_kv, d):
+    """Rows of a packed q/k/v matrix as the decode projection kernel wants them: in each q and
+    k head, dims 8t..8t+7 followed by d/2+8t..d/2+8t+7; v heads in natural order."""
+    rows = []
+    for h in range(n_q + n_kv):
+        for t in range(d // 16):
+            rows += [h * d + 8 * t + i for i in range(8)] + [h * d + d // 2 + 8 * t + i for i in range(8)]
+    return torch.tensor(rows + list(range((n_q + n_kv) * d, (n_q + 2 * n_kv) * d)))
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,bs,Kd", [(12, 2, 128, 16, 1536), (6, 2, 48, 4, 96), (3, 1, 32, 16, 96),
+                                              (7, 7, 16, 8, 64), (28, 4, 128, 32, 224)])
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+def test_decode_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
+    """q/k/v product + bias + rotation + cache append in one kernel (and the
+    separate rotary kernel on the same paired column order) against the plain
+    functions applied to the natural-order weights."""
+    g = torch.Generator().manual_seed(n_q * 100 + M)
+    bf = torch.bfloat16
+    N = (n_q + 2 * n_kv) * d
+    x = torch.randn(M, Kd, generator=g).to(bf)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(bf)
+    b = (0.5 * torch.randn(N, generator=g)).to(bf)
+    ctx = [int(v) for v in torch.randint(0, 50, (M,), generator=g)]
+    table, slots, total = scrambled_table([c + 1 for c in ctx], bs, M + 2, g)
+    theta, n_pos = 9999.0, 64
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2).float() / d))
+    fr = torch.outer(torch.arange(n_pos).float(), inv)
+    cos, sin = fr.cos().to(DEV), fr.sin().to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tok_row, tok_pos, row_slot = i32(list(range(M))), i32(ctx), i32(slots)
+    order = paired_order(n_q, n_kv, d)
+    wp, bp = w[order].contiguous().to(DEV), b[order].contiguous().to(DEV)
+
+    qkv = (P.linear(x.double(), w.double(), b.double())).view(M, n_q + 2 * n_kv, d)
+    c2, s2 = P.rope_tables(d, n_pos, theta)
+    rot = P.apply_rope(qkv[:, :n_q + n_kv], c2[torch.tensor(ctx)], s2[torch.tensor(ctx)])
+
+    def check(q_out, kp, vp, tol):
+        assert rel(q_out.view(M, n_q, d), rot[:, :n_q]) < tol
+        for m in range(M):
+            blk = int(table[slots[m], ctx[m] // bs])
+            assert rel(kp[blk, :, ctx[m] % bs], rot[m, n_q:]) < tol
+            assert rel(vp[blk, :, ctx[m] % bs], qkv[m, n_q + n_kv:]) < tol
+
+    for splits in sorted({1, K.gemv_splits(M, N, Kd, 592)}):
+        kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
+        vp = torch.zeros_like(kp)
+        q_out = torch.zeros(M, n_q * d, dtype=bf, device=DEV)
+        st = status()
+        K.gemv_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp, table.to(DEV),
+                        n_q, n_kv, d, True, st, splits)
+        assert int(st.item()) == 0
+        check(q_out, kp, vp, 6e-3)
+        assert int((kp != 0).sum().item()) <= M * n_kv * d            # only this step's positions were written
+    # the separate kernel on a projection whose columns are in the paired order
+    proj = (x.double() @ wp.double().cpu().T + bp.double().cpu()).to(bf).to(DEV)
+    kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.zeros(M, n_q * d, dtype=bf, device=DEV)
+    K.rope_append(proj, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp, table.to(DEV), n_q, n_kv, d, True,
+                  status(), paired=True)
+    check(q_out, kp, vp, 1e-2)
+    # a padding row writes nothing
+    kp.zero_()
+    K.gemv_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, i32([-1] * M), kp, vp, table.to(DEV),
+                    n_q, n_kv, d, True, status(), 1)
+    assert float(kp.abs().max()) == 0.0
 
 
 def attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window):
