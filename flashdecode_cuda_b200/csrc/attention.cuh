@@ -28,5 +28,7 @@ struct AttnParams {
 // decode steps (one new token per row) on the tensor cores; returns 1 if it
 // does not take the sizes (the caller then uses the CUDA-core kernel)
 int launch_attn_decode_mma(const AttnParams& p, int n_rows, cudaStream_t stream);
+// prompt steps (several new tokens per row) on the tensor cores; same return convention
+int launch_attn_prefill_mma(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream);
 
 }  // namespace fd

@@ -241,12 +241,18 @@ attn_tile_kernel(const AttnParams p) {
 
 // Merge the per-split triples of every (token, query head): m = max m_s,
 // l = sum l_s e^(m_s - m), out = sum acc_s e^(m_s - m) / l.  Splits that saw
-// no key (l_s == 0) are skipped; a padding row gives zeros.
+// no key (l_s == 0) are skipped; a padding row gives zeros.  The weights
+// e^(m_s - m) / l are computed once per (token, head) into shared memory; then
+// a thread owns one output dim and sums over the splits with independent loads.
+constexpr int COMBINE_MAX_SPLITS = 512;
+
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
                                     const float* __restrict__ part_acc, T* __restrict__ out,
                                     const int* __restrict__ tok_row, const int* __restrict__ row_slot,
                                     int n_q, int d, int n_splits) {
+    __shared__ float w_s[COMBINE_MAX_SPLITS];
+    __shared__ float red[33];
     const int tok = blockIdx.y, h = blockIdx.x;
     const size_t row = (size_t)tok * n_q + h;
     T* o = out + row * d;
@@ -256,17 +262,38 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
     }
     const float* pm = part_m + row * n_splits;
     const float* pl = part_l + row * n_splits;
+    // block-wide max of m over the splits that saw a key
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; ++s)
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x)
         if (pl[s] > 0.f) m = fmaxf(m, pm[s]);
-    float l = 0.f;
-    for (int s = 0; s < n_splits; ++s)
-        if (pl[s] > 0.f) l += pl[s] * expf(pm[s] - m);
+    m = warp_max(m);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = -INFINITY;
+    for (int w = 0; w < nwarps; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    // weights and their sum, in split order within a thread; the block sum order is fixed too
+    float lsum = 0.f;
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+        const float ls = pl[s];
+        const float w = ls > 0.f ? expf(pm[s] - m) : 0.f;
+        w_s[s] = w;
+        lsum += ls * w;
+    }
+    const float l = block_sum(lsum, red);
     const float inv = l > 0.f ? 1.f / l : 0.f;
+    const float* pa = part_acc + row * n_splits * d;
     for (int j = threadIdx.x; j < d; j += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < n_splits; ++s)
-            if (pl[s] > 0.f) a += part_acc[(row * n_splits + s) * d + j] * expf(pm[s] - m);
+        int s = 0;
+        for (; s + 4 <= n_splits; s += 4) {
+            const float a0 = pa[(size_t)(s + 0) * d + j], a1 = pa[(size_t)(s + 1) * d + j];
+            const float a2 = pa[(size_t)(s + 2) * d + j], a3 = pa[(size_t)(s + 3) * d + j];
+            a = fmaf(a0, w_s[s], a); a = fmaf(a1, w_s[s + 1], a);
+            a = fmaf(a2, w_s[s + 2], a); a = fmaf(a3, w_s[s + 3], a);
+        }
+        for (; s < n_splits; ++s) a = fmaf(pa[(size_t)s * d + j], w_s[s], a);
         o[j] = from_float<T>(a * inv);
     }
 }
@@ -324,7 +351,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     FD_REQUIRE(d % 16 == 0 && d >= 16 && d <= 256, -2, "attention: head size %d must be a multiple of 16 in [16, 256]", d);
     FD_REQUIRE(G <= RMAX, -2, "attention: group size %d exceeds %d", G, RMAX);
     FD_REQUIRE(block_size > 0, -2, "attention: block size %d", block_size);
-    FD_REQUIRE(n_splits >= 1, -2, "attention: n_splits=%d", n_splits);
+    FD_REQUIRE(n_splits >= 1 && n_splits <= COMBINE_MAX_SPLITS, -2, "attention: n_splits=%d (1..%d)", n_splits, COMBINE_MAX_SPLITS);
     FD_REQUIRE(n_splits == 1 || (split_len > 0 && split_len % KT == 0), -2,
                "attention: split length %d must be a positive multiple of %d", split_len, KT);
     FD_REQUIRE(n_splits == 1 || scratch != nullptr, -2, "attention: split form needs scratch memory");
@@ -351,6 +378,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
 
     int rc = 1;
     if (use_mma && dtype == 1 && max_q_len == 1) rc = launch_attn_decode_mma(p, n_rows, stream);
+    else if (use_mma && dtype == 1) rc = launch_attn_prefill_mma(p, n_rows, max_q_len, stream);
     if (rc == 1)
         rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
                         : launch_attn<bf16>(p, n_rows, max_q_len, stream);

@@ -22,7 +22,7 @@ def plan_splits(n_rows: int, n_kv: int, kv_len_bound: int, sm_count: int):
     ctas = max(1, n_rows * n_kv)
     want = max(1, (2 * sm_count) // ctas)
     split_len = -(-kv_len_bound // want)
-    split_len = max(64, -(-split_len // 32) * 32)
+    split_len = max(128, -(-split_len // 32) * 32)
     n_splits = max(1, -(-kv_len_bound // split_len))
     return n_splits, split_len
 

@@ -22,7 +22,7 @@ def _qwen2(**kw) -> dict:
     return base
 
 
-# Three tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option.
 TINY = {
     # 2 layers, group 2, head_dim = hidden/heads, tied head, powers of two
     "A": _qwen2(num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
@@ -37,6 +37,10 @@ TINY = {
                 head_dim=48, intermediate_size=176, vocab_size=333, rope_theta=500000.0, rms_norm_eps=3e-6,
                 tie_word_embeddings=False, max_position_embeddings=512, use_sliding_window=True,
                 sliding_window=24, max_window_layers=2),
+    # head_dim 64 with group 3: the size at which the tensor-core attention kernels take over
+    "D": _qwen2(num_hidden_layers=2, hidden_size=128, num_attention_heads=6, num_key_value_heads=2,
+                head_dim=64, intermediate_size=192, vocab_size=320, rope_theta=250000.0, rms_norm_eps=2e-6,
+                tie_word_embeddings=True, max_position_embeddings=1024),
 }
 NO_BIAS = {"C"}
 

@@ -482,6 +482,29 @@ def test_attention_decode_tensor_cores(n_q, n_kv, d, bs, n_splits, split_len):
         assert float(pad.float().abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,bs", [(12, 2, 128, 16), (7, 1, 128, 4), (5, 5, 64, 32), (6, 2, 64, 16), (28, 4, 128, 8)])
+def test_attention_prompts_tensor_cores(n_q, n_kv, d, bs):
+    """The dispatcher's tensor-core kernel for bfloat16 prompt steps: unequal
+    lengths around the 64-token tile edges, some continuing a cached prefix."""
+    got, want, _ = run_attention("bfloat16", n_q, n_kv, d, bs, ctx=[0, 0, 13, 0, 100, 64], new=[1, 64, 65, 130, 30, 63],
+                                 fn=K.attention)
+    assert rel(got, want) < TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("window", [1, 5, 63, 64, 65, 200])
+def test_attention_prompts_tensor_cores_window_and_far_key(window):
+    got, want, _ = run_attention("bfloat16", 6, 2, 64, 16, ctx=[0, 90, 7], new=[150, 70, 1], window=window, fn=K.attention)
+    assert rel(got, want) < TOL["bfloat16"]
+    if window == 200:
+        for key_pos in (0, 63, 64, 400, 639, 698):
+            got, want, _ = run_attention("bfloat16", 12, 2, 128, 16, ctx=[0, 0], new=[700, 3], spike=(0, key_pos),
+                                         fn=K.attention)
+            assert rel(got, want) < TOL["bfloat16"], key_pos
+            got, want, _ = run_attention("bfloat16", 12, 2, 128, 16, ctx=[640, 0], new=[60, 3], spike=(0, key_pos),
+                                         fn=K.attention)
+            assert rel(got, want) < TOL["bfloat16"], key_pos
+
+
 @pytest.mark.parametrize("window", [1, 16, 17, 100])
 def test_attention_decode_tensor_cores_window_and_far_key(window):
     got, want, _ = run_attention("bfloat16", 6, 2, 128, 16, ctx=[200, 40, 7], new=[1, 1, 1], window=window,

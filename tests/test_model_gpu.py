@@ -11,7 +11,7 @@ from helpers import TINY, TOL, oracle_logits, prompts_for, rel_err, write_folder
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = ["A", "B", "C"]
+CONFIGS = ["A", "B", "C", "D"]
 DTYPES = ["float32", "bfloat16"]
 
 
@@ -27,7 +27,7 @@ def engines(folders):
 
 
 def _lengths(name):
-    return {"A": [5, 11, 17, 64], "B": [1, 7, 16, 33, 100], "C": [3, 24, 25, 49, 130]}[name]
+    return {"A": [5, 11, 17, 64], "B": [1, 7, 16, 33, 100], "C": [3, 24, 25, 49, 130], "D": [2, 63, 64, 65, 200]}[name]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -97,7 +97,7 @@ def test_unequal_batches_one_after_another(engines, folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
 def test_long_decoding(engines, folders, name, dtype):
     """Two tokens of prompt, then 200 decoded one by one in a batch of two."""
     eng = engines[(name, dtype)]
