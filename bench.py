@@ -260,7 +260,11 @@ def main() -> int:
     if args.prefill_only:
         if args.profile_range:
             torch.cuda.profiler.start()
-        print(json.dumps({"prefill": prefill_run(engine, cfg, 2048, 1 if args.profile_range else warmup, args.seed, pk)}))
+        res = prefill_run(engine, cfg, 2048, 1 if args.profile_range else warmup, args.seed, pk)
+        if args.profile_range:
+            torch.cuda.profiler.stop()
+        clocks.stop()                      # a child left running would keep a profiler waiting for it
+        print(json.dumps({"prefill": res}))
         return 0
     prange = (args.prompt_min or args.context // 4, args.prompt_max or args.context // 2)
     main_run = decode_run(engine, args.batch, args.context, args.steps, warmup, args.seed, e2e=False,

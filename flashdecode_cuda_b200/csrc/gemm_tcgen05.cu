@@ -1,0 +1,352 @@
+// Matrix product for prompt steps on the 5th-generation tensor cores:
+//     out[M, N] = x[M, K] W[N, K]^T (+ bias | gated SiLU)      bfloat16 in, float accumulate
+//
+// One CTA computes one 128 x 128 tile of the output.
+//  * warp 0 (one lane): TMA producer.  `cp.async.bulk.tensor.2d` brings 128 x 64
+//    tiles of x and of W into shared memory in the 128-byte-swizzled layout, four
+//    stages deep, each stage announced on an mbarrier (expect_tx / complete_tx).
+//  * warp 1 (one lane): MMA issuer.  For every stage it issues four
+//    `tcgen05.mma.cta_group::1.kind::f16` (M 128, N 128, K 16) whose operands are
+//    shared-memory descriptors and whose accumulator lives in tensor memory
+//    (128 lanes x 128 columns of float); `tcgen05.commit` hands the stage back to
+//    the producer and, after the last one, tells the epilogue the tile is done.
+//  * warps 2-5: epilogue.  Each reads its quarter of the accumulator with
+//    `tcgen05.ld.32x32b` (a thread gets 32 consecutive columns of one row), adds
+//    the bias or applies silu(gate) * up, rounds once and stores.
+// Rows of x beyond M, rows of W beyond N and columns beyond K are zero-filled by
+// the TMA unit, so any M, N and any K that is a multiple of 8 are taken.
+//
+// Every wait on an mbarrier is bounded in time: if one runs out, the CTA sets
+// a bit in the status word, every role leaves its loop, tensor memory is freed
+// and the kernel returns (wrong output, a reported error, no hang).
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace fd {
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_THREADS = 192;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;          // 16 KB
+constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;          // 16 KB
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr unsigned long long TC_WAIT_NS = 200ull * 1000 * 1000;   // 0.2 s per wait, then give up
+
+struct TcParams {
+    const void* bias;      // [N] or null
+    void* out;
+    int* status;
+    int M, N, K;
+    int mode;              // 1: bf16 [M, N]; 2: float [M, N]; 3: gated, bf16 [M, N / 2]
+    int bias_f32;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------
+__device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait for the phase with the given parity.  False: the time ran out (or another
+// thread already gave up); the caller leaves its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > TC_WAIT_NS) {
+            *abort_flag = 1;
+            set_status(status, STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t v[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, laid out
+// by TMA with the 128-byte swizzle: 8-row groups of 1024 bytes (SBO), version 1, layout 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);       // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                       // leading byte offset: not used by swizzled K-major layouts
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                       // 128-byte swizzle
+    return d;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                    const TcParams p) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TC_STAGES * TC_STAGE_BYTES);
+    // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * TC_STAGES + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
+    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        abort_flag[0] = 0;
+        abort_flag[1] = 0;        // private flag of the producer's drain loop
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(s_addr(&bars[s]), 1);
+            mbar_init(s_addr(&bars[TC_STAGES + s]), 1);
+        }
+        mbar_init(s_addr(&bars[2 * TC_STAGES]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // 128 columns of tensor memory for the float accumulator (power of two >= 32)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer ----
+        int issued = 0;
+        for (int it = 0; it < k_iters; ++it) {
+            const int s = it % TC_STAGES;
+            if (it >= TC_STAGES &&
+                !mbar_wait(s_addr(&bars[TC_STAGES + s]), ((it / TC_STAGES) - 1) & 1, abort_flag, p.status)) break;
+            if (*abort_flag) break;
+            const uint32_t full = s_addr(&bars[s]);
+            mbar_expect_tx(full, TC_STAGE_BYTES);
+            unsigned char* a = tiles + s * TC_STAGE_BYTES;
+            tma_load_2d(s_addr(a), &map_x, full, it * TC_BK, m0);
+            tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, full, it * TC_BK, n0);
+            issued = it + 1;
+        }
+        if (*abort_flag) {
+            // let the copies already under way land before the CTA goes away
+            for (int it = max(0, issued - TC_STAGES); it < issued; ++it)
+                mbar_wait(s_addr(&bars[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag + 1, nullptr);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        // instruction descriptor: D float, A and B bf16, both K-major, N / 8, M / 16
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        for (int it = 0; it < k_iters; ++it) {
+            const int s = it % TC_STAGES;
+            if (!mbar_wait(s_addr(&bars[s]), (it / TC_STAGES) & 1, abort_flag, p.status)) break;
+            tc_fence_after();
+            const uint32_t a = s_addr(tiles + s * TC_STAGE_BYTES);
+            const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < TC_BK / 16; ++kk)        // 32 bytes further along the swizzled row per K = 16
+                tc_mma(tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (it | kk) != 0);
+            tc_commit(s_addr(&bars[TC_STAGES + s]));        // the stage is free once these MMAs have read it
+        }
+        tc_commit(s_addr(&bars[2 * TC_STAGES]));            // the accumulator is complete
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w may touch lanes 32 (w % 4) .. + 32 of tensor memory ----
+        const int quarter = warp & 3;
+        const int m = m0 + quarter * 32 + lane;
+        // all lanes of a warp must agree before the warp-wide tensor-memory loads
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&bars[2 * TC_STAGES]), 0, abort_flag, p.status));
+        tc_fence_after();
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+                uint32_t v[32];
+                tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
+                tc_wait_ld();
+                const int n = n0 + c0;
+                if (m >= p.M || n >= p.N) continue;
+                if (p.mode == 3) {
+                    // 32 columns = two tiles of 8 gate + 8 up values -> 16 outputs
+                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * (p.N >> 1) + (n >> 1);
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        if (n + t * 16 >= p.N) break;
+                        __align__(16) __nv_bfloat16 r[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g = __uint_as_float(v[t * 16 + j]), u = __uint_as_float(v[t * 16 + 8 + j]);
+                            r[j] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+                        }
+                        *reinterpret_cast<uint4*>(o + t * 8) = *reinterpret_cast<const uint4*>(r);
+                    }
+                    continue;
+                }
+                const int cols = min(32, p.N - n);
+                float f[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    f[j] = __uint_as_float(v[j]);
+                    if (p.bias != nullptr && j < cols)
+                        f[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[n + j]
+                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n + j]);
+                }
+                if (p.mode == 1) {
+                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n;
+                    if (cols == 32 && (p.N & 7) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            __align__(16) __nv_bfloat16 r[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) r[e] = __float2bfloat16_rn(f[j + e]);
+                            *reinterpret_cast<uint4*>(o + j) = *reinterpret_cast<const uint4*>(r);
+                        }
+                    } else {
+                        for (int j = 0; j < cols; ++j) o[j] = __float2bfloat16_rn(f[j]);
+                    }
+                } else {
+                    float* o = static_cast<float*>(p.out) + (size_t)m * p.N + n;
+                    if (cols == 32 && (p.N & 3) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                    } else {
+                        for (int j = 0; j < cols; ++j) o[j] = f[j];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// Tensor map of a row-major bf16 matrix [rows, cols] read in boxes of 128 rows x 64 columns
+// with the 128-byte swizzle.  Maps are cached by (address, shape): weights and workspace
+// buffers keep their addresses.
+static int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out) {
+    static std::map<std::tuple<const void*, int, int>, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    auto key = std::make_tuple(ptr, rows, cols);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return fail(-4, "gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(-4, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d for a %d x %d matrix", (int)r, rows, cols);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return 0;
+}
+
+}  // namespace fd
+
+using namespace fd;
+
+// 1 if the tensor-core product takes these sizes (K a multiple of 8, enough rows to be worth a
+// 128-row tile), else 0.
+extern "C" int fd_gemm_tc_supported(int M, int N, int K) {
+    return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && encode_fn() != nullptr;
+}
+
+// mode 1: out bf16 [M, N] (+ bias); 2: out float [M, N] (+ bias); 3: W rows in tiles of 8 gate +
+// 8 up rows, out bf16 [M, N / 2] = silu(gate) * up (N a multiple of 16).
+extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bias_f32, void* out, int mode,
+                          int M, int N, int K, int* status, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    FD_REQUIRE(mode >= 1 && mode <= 3, -2, "gemm_tcgen05: mode %d", mode);
+    FD_REQUIRE(mode != 3 || N % 16 == 0, -2, "gemm_tcgen05: the gated form needs N (= 2 x outputs) to be a multiple of 16, got %d", N);
+    FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0, -2,
+               "gemm_tcgen05: x, W and out must be 16-byte aligned");
+    CUtensorMap mx, mw;
+    int rc = tensor_map(x, M, K, &mx);
+    if (rc != 0) return rc;
+    rc = tensor_map(w, N, K, &mw);
+    if (rc != 0) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        if (e != cudaSuccess) return fail(-3, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", TC_SMEM, cudaGetErrorString(e));
+        configured = true;
+    }
+    TcParams p;
+    p.bias = bias; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = bias_f32;
+    dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
+    FD_REQUIRE(grid.y <= 65535, -2, "gemm_tcgen05: M=%d too large for one launch", M);
+    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(mx, mw, p);
+    return check_launch("gemm_tcgen05");
+}

@@ -75,6 +75,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_silu_mul": [P, P, I, I, I, I, P],
         "fd_rope_append": [P, I, I, LL, P, I, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+        "fd_gemm_tc_supported": [I, I, I],
+        "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
         "fd_gemv_splits": [I, I, I, I, I],
         "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P],
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
@@ -218,6 +220,29 @@ def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
 
 
 GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
+
+
+def gemm_tc_supported(M: int, N: int, K: int) -> bool:
+    return bool(lib().fd_gemm_tc_supported(M, N, K))
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, gated: bool = False,
+            status: Optional[torch.Tensor] = None) -> None:
+    """out = x w^T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulator in
+    tensor memory); bfloat16 operands, ``out`` bfloat16 or float32 [M, N], or
+    with ``gated`` (w rows in tiles of 8 gate + 8 up) bfloat16 [M, N / 2] =
+    silu(gate) * up.  Any M and N; K a multiple of 8."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K
+    if gated:
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and bias is None
+        mode = GEMV_GATED
+    else:
+        assert out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32)
+        mode = GEMV_BF16 if out.dtype == torch.bfloat16 else GEMV_F32
+    _check(lib().fd_gemm_tc(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                            _ptr(out), mode, M, N, K, _ptr(status), _stream()))
 
 
 def gemv_splits(M: int, N: int, K: int, target_ctas: int, allow_split: bool = True) -> int:

@@ -178,6 +178,36 @@ def test_gemv_refuses_what_it_cannot_do():
                torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV), K.GEMV_BF16)
 
 
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (128, 256, 256), (130, 200, 72), (70, 333, 1536), (2048, 2048, 1536),
+                                    (300, 1536, 8960), (17, 16, 8)])
+def test_gemm_tcgen05(M, N, K_):
+    """The TMA + tcgen05 product of prompt steps: full tiles, ragged edges in M, N
+    and K (zero-filled by TMA), bias in either dtype, float output."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    want = P.linear(x.double(), w.double())
+    assert K.gemm_tc_supported(M, N, K_)
+    st = status()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.gemm_tc(x, w, None, out, status=st)
+    assert rel(out, want) < 5e-3
+    K.gemm_tc(x, w, b, out, status=st)
+    assert rel(out, want + b.double()) < 5e-3
+    out32 = torch.full((M, N), float("nan"), device=DEV)
+    K.gemm_tc(x, w, b.float(), out32, status=st)
+    assert rel(out32, want + b.double()) < 2e-5
+    assert int(st.item()) == 0
+    if N % 16 == 0:
+        I = N // 2
+        gate, up = w[:I], w[I:]
+        tiled = torch.stack([gate.view(I // 8, 8, K_), up.view(I // 8, 8, K_)], dim=1).reshape(N, K_).contiguous()
+        act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K.gemm_tc(x, tiled, None, act, gated=True, status=st)
+        assert rel(act, P.swiglu(P.linear(x.double(), gate.double()), P.linear(x.double(), up.double()))) < 6e-3
+
+
 def test_gemm_simt_rows_do_not_depend_on_the_batch():
     """The same row gives the same bits alone and among 100 others."""
     g = torch.Generator().manual_seed(5)
