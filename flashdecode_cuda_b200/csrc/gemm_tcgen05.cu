@@ -3,8 +3,10 @@
 //
 // One CTA computes one 128 x 128 tile of the output.
 //  * warp 0 (one lane): TMA producer.  `cp.async.bulk.tensor.2d` brings 128 x 64
-//    tiles of x and of W into shared memory in the 128-byte-swizzled layout, four
+//    tiles of x and of W into shared memory in the 128-byte-swizzled layout, three
 //    stages deep, each stage announced on an mbarrier (expect_tx / complete_tx).
+//    Three stages (97 KB) let two CTAs share an SM, so one CTA's epilogue runs
+//    under the other's main loop; each takes 128 of the 512 tensor-memory columns.
 //  * warp 1 (one lane): MMA issuer.  For every stage it issues four
 //    `tcgen05.mma.cta_group::1.kind::f16` (M 128, N 128, K 16) whose operands are
 //    shared-memory descriptors and whose accumulator lives in tensor memory
@@ -29,7 +31,7 @@
 
 namespace fd {
 
-constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 64, TC_STAGES = 3;
 constexpr int TC_THREADS = 192;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;          // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;          // 16 KB
@@ -121,7 +123,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const TcParams p) {
     extern __shared__ unsigned char tc_smem_raw[];
@@ -208,42 +210,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const int n = n0 + c0;
                 if (m >= p.M || n >= p.N) continue;
                 if (p.mode == 3) {
-                    // 32 columns = two tiles of 8 gate + 8 up values -> 16 outputs
+                    // 32 columns = two tiles of 8 gate + 8 up values -> 16 outputs (N is a multiple of 16)
                     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * (p.N >> 1) + (n >> 1);
+                    uint32_t packed[8];
 #pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        if (n + t * 16 >= p.N) break;
-                        __align__(16) __nv_bfloat16 r[8];
+                    for (int t = 0; t < 2; ++t)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float g = __uint_as_float(v[t * 16 + j]), u = __uint_as_float(v[t * 16 + 8 + j]);
-                            r[j] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+                        for (int j = 0; j < 8; j += 2) {
+                            const float g0 = __uint_as_float(v[t * 16 + j]), u0 = __uint_as_float(v[t * 16 + 8 + j]);
+                            const float g1 = __uint_as_float(v[t * 16 + j + 1]), u1 = __uint_as_float(v[t * 16 + 9 + j]);
+                            const __nv_bfloat162 r = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0,
+                                                                           g1 / (1.f + __expf(-g1)) * u1);
+                            packed[t * 4 + (j >> 1)] = *reinterpret_cast<const uint32_t*>(&r);
                         }
-                        *reinterpret_cast<uint4*>(o + t * 8) = *reinterpret_cast<const uint4*>(r);
-                    }
+                    *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    if (n + 16 < p.N) *reinterpret_cast<uint4*>(o + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                     continue;
                 }
                 const int cols = min(32, p.N - n);
                 float f[32];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    f[j] = __uint_as_float(v[j]);
-                    if (p.bias != nullptr && j < cols)
-                        f[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[n + j]
-                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n + j]);
+                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int nn = min(n + j, p.N - 1);
+                        f[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[nn]
+                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[nn]);
+                    }
                 }
                 if (p.mode == 1) {
                     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n;
                     if (cols == 32 && (p.N & 7) == 0) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
-                            __align__(16) __nv_bfloat16 r[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) r[e] = __float2bfloat16_rn(f[j + e]);
-                            *reinterpret_cast<uint4*>(o + j) = *reinterpret_cast<const uint4*>(r);
+                            const __nv_bfloat162 r0 = __floats2bfloat162_rn(f[j], f[j + 1]), r1 = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
+                            const __nv_bfloat162 r2 = __floats2bfloat162_rn(f[j + 4], f[j + 5]), r3 = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
+                            *reinterpret_cast<uint4*>(o + j) = make_uint4(*reinterpret_cast<const uint32_t*>(&r0), *reinterpret_cast<const uint32_t*>(&r1),
+                                                                          *reinterpret_cast<const uint32_t*>(&r2), *reinterpret_cast<const uint32_t*>(&r3));
                         }
                     } else {
-                        for (int j = 0; j < cols; ++j) o[j] = __float2bfloat16_rn(f[j]);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < cols) o[j] = __float2bfloat16_rn(f[j]);
                     }
                 } else {
                     float* o = static_cast<float*>(p.out) + (size_t)m * p.N + n;
@@ -252,7 +261,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         for (int j = 0; j < 32; j += 4)
                             *reinterpret_cast<float4*>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
                     } else {
-                        for (int j = 0; j < cols; ++j) o[j] = f[j];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < cols) o[j] = f[j];
                     }
                 }
             }
