@@ -27,7 +27,9 @@ __global__ void __launch_bounds__(PM_THREADS)
 attn_prefill_mma_kernel(const AttnParams p) {
     constexpr int CPR = D / 8;                      // 16-byte chunks per row
     constexpr int TILE_BYTES = PM_BN * D * 2;
-    const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    // the last query tiles of a sequence see the most keys: schedule them first, so that the
+    // short tiles fill the tail of the launch instead of the long ones
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int slot = p.row_slot[b];
     if (slot < 0) return;
     const int q_len = p.row_q_len[b];
@@ -50,6 +52,7 @@ attn_prefill_mma_kernel(const AttnParams p) {
     const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(p.k_pool);
     const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(p.v_pool);
     const int bs = p.block_size;
+    const int bs_shift = (bs & (bs - 1)) == 0 ? __ffs(bs) - 1 : -1;     // block sizes that are powers of two: shift and mask
 
     // queries of the tile (rows beyond nq as zeros)
 #pragma unroll
@@ -72,11 +75,13 @@ attn_prefill_mma_kernel(const AttnParams p) {
             const __nv_bfloat16* vsrc = vp;
             int bytes = 0;
             if (t >= lo && t < hi) {
-                const int blk = p.block_table[(size_t)slot * p.max_blocks + t / bs];
+                const int col = bs_shift >= 0 ? t >> bs_shift : t / bs;
+                const int in_blk = bs_shift >= 0 ? t & (bs - 1) : t - col * bs;
+                const int blk = p.block_table[(size_t)slot * p.max_blocks + col];
                 if (blk < 0 || blk >= p.num_blocks) {
                     set_status(p.status, STATUS_BAD_BLOCK);
                 } else {
-                    const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + (t % bs)) * D + cc * 8;
+                    const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + in_blk) * D + cc * 8;
                     ksrc = kp + off;
                     vsrc = vp + off;
                     bytes = 16;

@@ -44,8 +44,25 @@ struct TcParams {
     void* out;
     int* status;
     int M, N, K;
-    int mode;              // 1: bf16 [M, N]; 2: float [M, N]; 3: gated, bf16 [M, N / 2]
+    int mode;              // 1: bf16 [M, N]; 2: float [M, N]; 3: gated, bf16 [M, N / 2];
+                           // 4: q/k/v projection with rotary encoding and cache append (TcRope)
     int bias_f32;
+};
+
+// Mode 4: the rows of W (columns of the product) are the q heads, the k heads, then the v
+// heads; inside a q or k head they come in tiles of 16: dims 8t .. 8t+7, then their rotation
+// partners d/2 + 8t .. d/2 + 8t+7; v heads in natural order.  `out` is q_out [M, n_q d].
+struct TcRope {
+    const float* cos_t;          // [table_len, d/2]
+    const float* sin_t;
+    const int* tok_row;          // [M]
+    const int* tok_pos;          // [M]
+    const int* row_slot;
+    __nv_bfloat16* k_pool;       // [num_blocks, n_kv, block_size, d]
+    __nv_bfloat16* v_pool;
+    const int* block_table;
+    int table_len, max_blocks, num_blocks, block_size;
+    int n_q, n_kv, d, write_kv;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -125,7 +142,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 
 __global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    const TcParams p) {
+                    const TcParams p, const TcRope ra) {
     extern __shared__ unsigned char tc_smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -201,6 +218,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // all lanes of a warp must agree before the warp-wide tensor-memory loads
         const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&bars[2 * TC_STAGES]), 0, abort_flag, p.status));
         tc_fence_after();
+        // mode 4: where this thread's token lives
+        int tok_slot = -1, tok_pos = 0;
+        size_t kv_off = 0;
+        bool kv_ok = false;
+        if (p.mode == 4 && m < p.M) {
+            tok_slot = ra.row_slot[ra.tok_row[m]];
+            tok_pos = ra.tok_pos[m];
+            if (tok_slot >= 0) {
+                if (tok_pos < 0 || tok_pos >= ra.table_len) {
+                    set_status(p.status, STATUS_BAD_POSITION);
+                    tok_slot = -1;
+                } else if (ra.write_kv) {
+                    const int blk = ra.block_table[(size_t)tok_slot * ra.max_blocks + tok_pos / ra.block_size];
+                    if (blk < 0 || blk >= ra.num_blocks) {
+                        set_status(p.status, STATUS_BAD_BLOCK);
+                    } else {
+                        kv_off = ((size_t)blk * ra.n_kv * ra.block_size + tok_pos % ra.block_size) * ra.d;
+                        kv_ok = true;
+                    }
+                }
+            }
+        }
         if (ok) {
 #pragma unroll 1
             for (int c0 = 0; c0 < TC_BN; c0 += 32) {
@@ -209,6 +248,68 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 tc_wait_ld();
                 const int n = n0 + c0;
                 if (m >= p.M || n >= p.N) continue;
+                if (p.mode == 4) {
+                    if (tok_slot < 0) continue;                       // padding row or bad position
+                    const int d = ra.d, half = d >> 1;
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        const int col = n + t * 16;                      // first column of this tile of 16
+                        if (col >= p.N) break;
+                        const int head = col / d, in_head = col - head * d;
+                        float lo8[8], hi8[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            lo8[j] = __uint_as_float(v[t * 16 + j]);
+                            hi8[j] = __uint_as_float(v[t * 16 + 8 + j]);
+                        }
+                        if (p.bias != nullptr) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                lo8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + j]
+                                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + j]);
+                                hi8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + 8 + j]
+                                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + 8 + j]);
+                            }
+                        }
+                        const bool is_v = head >= ra.n_q + ra.n_kv;
+                        int j_lo, j_hi;                                   // dims of the two groups of 8 inside the head
+                        if (is_v) {
+                            j_lo = in_head; j_hi = in_head + 8;
+                        } else {
+                            j_lo = (in_head >> 4) * 8; j_hi = j_lo + half;
+                            const float4* c4 = reinterpret_cast<const float4*>(ra.cos_t + (size_t)tok_pos * half + j_lo);
+                            const float4* s4 = reinterpret_cast<const float4*>(ra.sin_t + (size_t)tok_pos * half + j_lo);
+                            const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+                            const float cs[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+                            const float sn[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const float x1 = lo8[j], x2 = hi8[j];
+                                lo8[j] = x1 * cs[j] - x2 * sn[j];
+                                hi8[j] = x2 * cs[j] + x1 * sn[j];
+                            }
+                        }
+                        uint32_t pl[4], ph[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const __nv_bfloat162 a = __floats2bfloat162_rn(lo8[2 * j], lo8[2 * j + 1]);
+                            const __nv_bfloat162 b = __floats2bfloat162_rn(hi8[2 * j], hi8[2 * j + 1]);
+                            pl[j] = *reinterpret_cast<const uint32_t*>(&a);
+                            ph[j] = *reinterpret_cast<const uint32_t*>(&b);
+                        }
+                        __nv_bfloat16* dst;
+                        if (head < ra.n_q) {
+                            dst = static_cast<__nv_bfloat16*>(p.out) + ((size_t)m * ra.n_q + head) * d;
+                        } else {
+                            if (!kv_ok) continue;
+                            const int kvh = is_v ? head - ra.n_q - ra.n_kv : head - ra.n_q;
+                            dst = (is_v ? ra.v_pool : ra.k_pool) + kv_off + (size_t)kvh * ra.block_size * d;
+                        }
+                        *reinterpret_cast<uint4*>(dst + j_lo) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                        *reinterpret_cast<uint4*>(dst + j_hi) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                    }
+                    continue;
+                }
                 if (p.mode == 3) {
                     // 32 columns = two tiles of 8 gate + 8 up values -> 16 outputs (N is a multiple of 16)
                     __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * (p.N >> 1) + (n >> 1);
@@ -358,6 +459,46 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
     p.bias = bias; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = bias_f32;
     dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
     FD_REQUIRE(grid.y <= 65535, -2, "gemm_tcgen05: M=%d too large for one launch", M);
-    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(mx, mw, p);
+    TcRope ra = {};
+    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(mx, mw, p, ra);
     return check_launch("gemm_tcgen05");
+}
+
+// The q/k/v projection of a prompt step with bias, rotary encoding and the append to the
+// paged cache in its epilogue (mode 4; see TcRope for the row order W and bias must have).
+extern "C" int fd_gemm_tc_qkv_rope(const void* x, const void* w, const void* bias, int bias_f32, void* q_out,
+                                   int M, int K, const float* cos_t, const float* sin_t, int table_len,
+                                   const int* tok_row, const int* tok_pos, const int* row_slot, void* k_pool,
+                                   void* v_pool, const int* block_table, int max_blocks, int num_blocks,
+                                   int block_size, int n_q, int n_kv, int d, int write_kv, int* status,
+                                   cudaStream_t stream) {
+    if (M == 0) return 0;
+    const int N = (n_q + 2 * n_kv) * d;
+    FD_REQUIRE(K >= 8 && K % 8 == 0, -2, "gemm_tcgen05: K=%d must be a multiple of 8 (16-byte rows for TMA)", K);
+    FD_REQUIRE(d >= 16 && d % 16 == 0, -2, "gemm_tc_qkv_rope: head size %d must be a multiple of 16", d);
+    FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
+               (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 && (uintptr_t)cos_t % 16 == 0 &&
+               (uintptr_t)sin_t % 16 == 0, -2, "gemm_tc_qkv_rope: all arrays must be 16-byte aligned");
+    CUtensorMap mx, mw;
+    int rc = tensor_map(x, M, K, &mx);
+    if (rc != 0) return rc;
+    rc = tensor_map(w, N, K, &mw);
+    if (rc != 0) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        if (e != cudaSuccess) return fail(-3, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", TC_SMEM, cudaGetErrorString(e));
+        configured = true;
+    }
+    TcParams p;
+    p.bias = bias; p.out = q_out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = 4; p.bias_f32 = bias_f32;
+    TcRope ra;
+    ra.cos_t = cos_t; ra.sin_t = sin_t; ra.tok_row = tok_row; ra.tok_pos = tok_pos; ra.row_slot = row_slot;
+    ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool; ra.block_table = block_table;
+    ra.table_len = table_len; ra.max_blocks = max_blocks; ra.num_blocks = num_blocks; ra.block_size = block_size;
+    ra.n_q = n_q; ra.n_kv = n_kv; ra.d = d; ra.write_kv = write_kv;
+    dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
+    FD_REQUIRE(grid.y <= 65535, -2, "gemm_tcgen05: M=%d too large for one launch", M);
+    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(mx, mw, p, ra);
+    return check_launch("gemm_tc_qkv_rope");
 }

@@ -77,6 +77,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemm_tc_supported": [I, I, I],
         "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
+        "fd_gemm_tc_qkv_rope": [P, P, P, I, P, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemv_splits": [I, I, I, I, I],
         "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P],
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
@@ -220,6 +221,24 @@ def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
 
 
 GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
+
+
+def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                     cos: torch.Tensor, sin: torch.Tensor, tok_row: torch.Tensor, tok_pos: torch.Tensor,
+                     row_slot: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                     n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor) -> None:
+    """The q/k/v projection of a prompt step on the tcgen05 tensor cores with
+    bias, rotary encoding and the append to the paged cache in its epilogue.
+    ``w`` and ``bias`` in the paired row order (see ``rope_append``)."""
+    M, K = x.shape
+    assert w.shape == ((n_q + 2 * n_kv) * head_dim, K) and q_out.shape == (M, n_q * head_dim)
+    assert x.dtype == w.dtype == q_out.dtype == k_pool.dtype == torch.bfloat16
+    num_blocks, _, block_size, _ = k_pool.shape
+    _check(lib().fd_gemm_tc_qkv_rope(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                                     _ptr(q_out), M, K, _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_row),
+                                     _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                     block_table.shape[1], num_blocks, block_size, n_q, n_kv, head_dim,
+                                     int(write_kv), _ptr(status), _stream()))
 
 
 def gemm_tc_supported(M: int, N: int, K: int) -> bool:

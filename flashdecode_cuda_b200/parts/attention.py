@@ -11,7 +11,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import KVRequest, LayerCache, Mixer, Runtime
-from .linear import GEMV_MAX_ROWS, matmul
+from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul
 
 
 def plan_splits(n_rows: int, n_kv: int, kv_len_bound: int, sm_count: int):
@@ -114,6 +114,10 @@ class GQAAttention(Mixer):
             K.gemv_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
                             lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status,
                             splits)
+        elif self.paired and x.dtype == torch.bfloat16 and fused_prompt_gemm(T, self.w_qkv.shape[0], self.hidden_size):
+            # prompts: the same fusion on the tcgen05 tensor cores
+            K.gemm_tc_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
+                               lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status)
         else:
             qkv = ws.get("qkv", (T, (self.n_q + 2 * self.n_kv) * d), x.dtype)
             matmul(x, self.w_qkv, self.b_qkv, qkv)

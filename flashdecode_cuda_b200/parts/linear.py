@@ -16,9 +16,21 @@ import torch
 from .. import kernels as K
 
 
+# Which kernel takes the bfloat16 products of prompt steps (more than GEMV_MAX_ROWS rows):
+#   "auto":    the library's own TMA + tcgen05 kernel where its fused epilogues pay for themselves
+#              (q/k/v with bias + rotation + cache append, gate/up with SiLU), cuBLAS for the plain
+#              products, where cuBLAS's 256-wide two-CTA tiles are still ahead (measured on B200);
+#   "tcgen05": the library's own kernel everywhere;  "cublas": cuBLAS everywhere.
+PROMPT_GEMM = "auto"
+
 # Up to this many rows the weight-streaming kernel beats the library product (measured on
 # B200 at the sizes of Qwen2.5-1.5B); above it the rows of x no longer fit the registers' reach.
 GEMV_MAX_ROWS = 16
+
+
+def fused_prompt_gemm(M: int, N: int, Kd: int) -> bool:
+    """Whether a prompt-step product with a fused epilogue goes to the tcgen05 kernel."""
+    return PROMPT_GEMM != "cublas" and K.gemm_tc_supported(M, N, Kd)
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -35,6 +47,9 @@ def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         if splits >= 1:
             K.gemv(x, w, bias, out, K.GEMV_F32 if out.dtype == torch.float32 else K.GEMV_BF16, splits)
             return out
+    if PROMPT_GEMM == "tcgen05" and K.gemm_tc_supported(M, w.shape[0], Kd):
+        K.gemm_tc(x, w, bias, out)
+        return out
     if out.dtype == torch.float32:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
         if bias is not None:

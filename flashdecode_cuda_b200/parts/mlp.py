@@ -10,7 +10,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import FeedForward, Runtime
-from .linear import GEMV_MAX_ROWS, matmul
+from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul
 
 
 @register_part("feed_forward", "swiglu")
@@ -52,6 +52,8 @@ class SwiGLU(FeedForward):
         if (self.tiled and x.dtype == torch.bfloat16 and T <= GEMV_MAX_ROWS
                 and K.gemv_splits(T, 2 * self.inter, self.hidden_size, 1, allow_split=False) == 1):
             K.gemv(x, self.w_gate_up, None, act, K.GEMV_GATED)          # product and silu(gate) * up in one kernel
+        elif self.tiled and x.dtype == torch.bfloat16 and fused_prompt_gemm(T, 2 * self.inter, self.hidden_size):
+            K.gemm_tc(x, self.w_gate_up, None, act, gated=True, status=self.rt.status)     # prompts: tcgen05, same fusion
         else:
             gu = ws.get("gate_up", (T, 2 * self.inter), x.dtype)
             matmul(x, self.w_gate_up, None, gu)

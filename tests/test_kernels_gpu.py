@@ -332,7 +332,7 @@ def paired_order(n_q, n_kv, d):
 @pytest.mark.parametrize("n_q,n_kv,d,bs,Kd", [(12, 2, 128, 16, 1536), (6, 2, 48, 4, 96), (3, 1, 32, 16, 96),
                                               (7, 7, 16, 8, 64), (28, 4, 128, 32, 224)])
 @pytest.mark.parametrize("M", [1, 5, 8, 16])
-def test_decode_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
+def test_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
     """q/k/v product + bias + rotation + cache append in one kernel (and the
     separate rotary kernel on the same paired column order) against the plain
     functions applied to the natural-order weights."""
@@ -374,6 +374,16 @@ def test_decode_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
         assert int(st.item()) == 0
         check(q_out, kp, vp, 6e-3)
         assert int((kp != 0).sum().item()) <= M * n_kv * d            # only this step's positions were written
+    # the same fusion in the tcgen05 kernel that prompt steps use
+    kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.zeros(M, n_q * d, dtype=bf, device=DEV)
+    st = status()
+    K.gemm_tc_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp, table.to(DEV),
+                       n_q, n_kv, d, True, st)
+    assert int(st.item()) == 0
+    check(q_out, kp, vp, 6e-3)
+    assert int((kp != 0).sum().item()) <= M * n_kv * d
     # the separate kernel on a projection whose columns are in the paired order
     proj = (x.double() @ wp.double().cpu().T + bp.double().cpu()).to(bf).to(DEV)
     kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
@@ -387,6 +397,46 @@ def test_decode_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
     K.gemv_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, i32([-1] * M), kp, vp, table.to(DEV),
                     n_q, n_kv, d, True, status(), 1)
     assert float(kp.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,bs,Kd", [(12, 2, 128, 16, 1536), (6, 2, 48, 4, 96), (5, 1, 64, 32, 72)])
+def test_prompt_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd):
+    """The tcgen05 q/k/v projection over two prompts (several 128-row tiles, a
+    ragged last one), one of them continuing a cached prefix, plus a padding row."""
+    g = torch.Generator().manual_seed(n_q)
+    bf = torch.bfloat16
+    N = (n_q + 2 * n_kv) * d
+    ctx, new = [0, 37], [170, 131]
+    T = sum(new) + 1                                  # one extra token belongs to a padding row
+    x = torch.randn(T, Kd, generator=g).to(bf)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(bf)
+    b = (0.5 * torch.randn(N, generator=g)).to(bf)
+    table, slots, total = scrambled_table([c + n for c, n in zip(ctx, new)], bs, 4, g)
+    theta, n_pos = 7777.0, 256
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2).float() / d))
+    fr = torch.outer(torch.arange(n_pos).float(), inv)
+    cos, sin = fr.cos().to(DEV), fr.sin().to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    rows = [r for r, n in enumerate(new) for _ in range(n)] + [2]
+    pos = [c + i for c, n in zip(ctx, new) for i in range(n)] + [0]
+    order = paired_order(n_q, n_kv, d)
+    kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
+    vp = torch.zeros_like(kp)
+    q_out = torch.zeros(T, n_q * d, dtype=bf, device=DEV)
+    st = status()
+    K.gemm_tc_qkv_rope(x.to(DEV), w[order].contiguous().to(DEV), b[order].contiguous().to(DEV), q_out, cos, sin,
+                       i32(rows), i32(pos), i32(slots + [-1]), kp, vp, table.to(DEV), n_q, n_kv, d, True, st)
+    assert int(st.item()) == 0
+    qkv = P.linear(x.double(), w.double(), b.double()).view(T, n_q + 2 * n_kv, d)
+    c2, s2 = P.rope_tables(d, n_pos, theta)
+    rot = P.apply_rope(qkv[:, :n_q + n_kv], c2[torch.tensor(pos)], s2[torch.tensor(pos)])
+    assert rel(q_out.view(T, n_q, d)[:-1], rot[:-1, :n_q]) < 6e-3
+    assert float(q_out[-1].float().abs().max()) == 0.0            # the padding row's token is left alone
+    for t in list(range(0, T - 1, 17)) + [T - 2]:
+        blk = int(table[slots[rows[t]], pos[t] // bs])
+        assert rel(kp[blk, :, pos[t] % bs], rot[t, n_q:]) < 6e-3
+        assert rel(vp[blk, :, pos[t] % bs], qkv[t, n_q + n_kv:]) < 6e-3
+    assert int((kp != 0).sum().item()) <= sum(new) * n_kv * d
 
 
 def attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window):
