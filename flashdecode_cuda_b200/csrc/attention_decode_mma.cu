@@ -34,6 +34,8 @@ attn_decode_mma_kernel(const AttnParams p) {
     constexpr int CPR = D / 8;                 // 16-byte chunks per row
     constexpr int TILE_BYTES = DM_TILE * D * 2;
     constexpr int WARP_BYTES = DM_STAGES * 2 * TILE_BYTES;   // K and V, two stages
+    pdl_launch_dependents();
+    pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int slot = p.row_slot[b];
     if (slot < 0) return;                       // padding row; the merge kernel writes its zeros
@@ -256,8 +258,7 @@ static int launch_dm(const AttnParams& p, int n_rows, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(p.n_splits, p.n_kv, n_rows);
-    k<<<grid, DM_THREADS, smem, stream>>>(p);
-    return check_launch("attention_decode_mma");
+    return launch("attention_decode_mma", k, grid, dim3(DM_THREADS), smem, stream, dim3(1, 1, 1), p);
 }
 
 int launch_attn_decode_mma(const AttnParams& p, int n_rows, cudaStream_t stream) {

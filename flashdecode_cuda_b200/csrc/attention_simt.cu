@@ -253,6 +253,8 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_m, const floa
                                     int n_q, int d, int n_splits) {
     __shared__ float w_s[COMBINE_MAX_SPLITS];
     __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tok = blockIdx.y, h = blockIdx.x;
     const size_t row = (size_t)tok * n_q + h;
     T* o = out + row * d;
@@ -385,12 +387,12 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     if (rc != 0 || n_splits == 1) return rc;
     dim3 grid(n_q, T);
     if (dtype == 0)
-        attn_combine_kernel<float><<<grid, 128, 0, stream>>>(p.part_m, p.part_l, p.part_acc, (float*)out,
-                                                            tok_row, row_slot, n_q, d, n_splits);
-    else
-        attn_combine_kernel<bf16><<<grid, 128, 0, stream>>>(p.part_m, p.part_l, p.part_acc, (bf16*)out,
-                                                           tok_row, row_slot, n_q, d, n_splits);
-    return check_launch("attention_combine");
+        return launch("attention_combine", attn_combine_kernel<float>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
+                      (const float*)p.part_m, (const float*)p.part_l, (const float*)p.part_acc, (float*)out, tok_row,
+                      row_slot, n_q, d, n_splits);
+    return launch("attention_combine", attn_combine_kernel<bf16>, grid, dim3(128), 0, stream, dim3(1, 1, 1),
+                  (const float*)p.part_m, (const float*)p.part_l, (const float*)p.part_acc, (bf16*)out, tok_row,
+                  row_slot, n_q, d, n_splits);
 }
 
 // The CUDA-core kernel for every case.

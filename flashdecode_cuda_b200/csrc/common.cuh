@@ -70,11 +70,59 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 }  // namespace fd
 
+namespace fd {
+
+// Programmatic dependent launch.  A kernel launched through fd::launch may begin while the
+// kernel before it in the stream is still running: it calls pdl_launch_dependents() at its
+// top (so the one after it can be set up early too), does what depends on nothing written by
+// earlier kernels (fetching weights), and calls pdl_wait() before it first touches anything an
+// earlier kernel wrote or still reads.  pdl_wait() returns once every earlier kernel has
+// completed and its writes are visible.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+}  // namespace fd
+
 // error reporting shared by the launchers (defined in runtime.cu)
 extern "C" const char* fd_last_error();
 namespace fd {
 int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
+}  // namespace fd
+
+namespace fd {
+extern int g_pdl;      // 1: launches carry the programmatic-serialization attribute (runtime.cu)
+
+// Launch with the attributes this library uses: programmatic dependent launch (when enabled)
+// and an optional thread-block cluster shape.
+template <typename... KArgs, typename... Args>
+inline int launch(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                  dim3 cluster, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int n = 0;
+    if (g_pdl) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster.x * cluster.y * cluster.z > 1) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = cluster.x;
+        attrs[n].val.clusterDim.y = cluster.y;
+        attrs[n].val.clusterDim.z = cluster.z;
+        ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    return 0;
+}
 }  // namespace fd
 
 #define FD_REQUIRE(cond, code, ...) \

@@ -13,6 +13,8 @@ namespace fd {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ resid, int H, int V, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = tokens[t];
     float* dst = resid + (size_t)t * H;
@@ -38,6 +40,8 @@ __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, int n_parts, si
                                    float* __restrict__ resid, int write_resid,
                                    const TW* __restrict__ w, float eps, TO* __restrict__ out,
                                    const int* __restrict__ rows, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float smem[];
     float* xs = smem;                 // H floats
     float* red = smem + ((H + 3) & ~3);  // 33 floats
@@ -59,6 +63,60 @@ __global__ void add_rmsnorm_kernel(const TD* __restrict__ delta, int n_parts, si
     TO* orow = out + (size_t)j * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x)
         orow[i] = from_float<TO>(xs[i] * rstd * to_float(w[i]));
+}
+
+// The same for rows that one CTA can hold in registers (H a multiple of 8, at most 8 * 1024):
+// bfloat16 delta and output, one 16-byte load per tensor per thread, every load (the norm
+// weight included) issued before the reduction.  This is the form decode steps use, where
+// the kernel's time is its chain of dependent memory accesses.
+template <typename TW>
+__global__ void add_rmsnorm_row_kernel(const __nv_bfloat16* __restrict__ delta, float* __restrict__ resid,
+                                       int write_resid, const TW* __restrict__ w, float eps,
+                                       __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const int j = blockIdx.x;
+    const int r = rows ? rows[j] : j;
+    const int i = threadIdx.x * 8;
+    float x[8], wv[8];
+    float ss = 0.f;
+    if (i < H) {
+        float* rrow = resid + (size_t)r * H + i;
+        const float4 r0 = *reinterpret_cast<const float4*>(rrow), r1 = *reinterpret_cast<const float4*>(rrow + 4);
+        x[0] = r0.x; x[1] = r0.y; x[2] = r0.z; x[3] = r0.w; x[4] = r1.x; x[5] = r1.y; x[6] = r1.z; x[7] = r1.w;
+        if (sizeof(TW) == 2) {
+            const uint4 wr = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + i);
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wr);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { wv[2 * e] = __low2float(w2[e]); wv[2 * e + 1] = __high2float(w2[e]); }
+        } else {
+            const float4 w0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i);
+            const float4 w1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i + 4);
+            wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+        }
+        if (delta != nullptr) {
+            const uint4 dr = *reinterpret_cast<const uint4*>(delta + (size_t)r * H + i);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dr);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { x[2 * e] += __low2float(d2[e]); x[2 * e + 1] += __high2float(d2[e]); }
+            if (write_resid) {
+                *reinterpret_cast<float4*>(rrow) = make_float4(x[0], x[1], x[2], x[3]);
+                *reinterpret_cast<float4*>(rrow + 4) = make_float4(x[4], x[5], x[6], x[7]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+    }
+    const float total = block_sum(ss, red);
+    if (i < H) {
+        const float rstd = rsqrtf(total / (float)H + eps);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(x[2 * e] * rstd * wv[2 * e], x[2 * e + 1] * rstd * wv[2 * e + 1]);
+        *reinterpret_cast<uint4*>(out + (size_t)j * H + i) = o;
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -193,10 +251,10 @@ extern "C" int fd_embed(const int* tokens, const void* table, int table_dtype, f
     FD_REQUIRE(H > 0 && V > 0, -2, "embed: bad sizes H=%d V=%d", H, V);
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == 0)
-        embed_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, resid, H, V, status);
-    else
-        embed_kernel<bf16><<<T, threads, 0, stream>>>(tokens, (const bf16*)table, resid, H, V, status);
-    return check_launch("embed");
+        return launch("embed", embed_kernel<float>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), tokens,
+                      (const float*)table, resid, H, V, status);
+    return launch("embed", embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, dim3(1, 1, 1), tokens,
+                  (const bf16*)table, resid, H, V, status);
 }
 
 template <typename TD, typename TO>
@@ -209,15 +267,14 @@ static int launch_norm(const void* delta, int n_parts, size_t part_stride, float
     if (w_dtype == 0) {
         auto k = add_rmsnorm_kernel<TD, float, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<n_out, threads, smem, stream>>>((const TD*)delta, n_parts, part_stride, resid, write_resid,
-                                            (const float*)w, eps, (TO*)out, rows, H);
+        return launch("add_rmsnorm", k, dim3(n_out), dim3(threads), smem, stream, dim3(1, 1, 1), (const TD*)delta, n_parts,
+                      part_stride, resid, write_resid, (const float*)w, eps, (TO*)out, rows, H);
     } else {
         auto k = add_rmsnorm_kernel<TD, bf16, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<n_out, threads, smem, stream>>>((const TD*)delta, n_parts, part_stride, resid, write_resid,
-                                            (const bf16*)w, eps, (TO*)out, rows, H);
+        return launch("add_rmsnorm", k, dim3(n_out), dim3(threads), smem, stream, dim3(1, 1, 1), (const TD*)delta, n_parts,
+                      part_stride, resid, write_resid, (const bf16*)w, eps, (TO*)out, rows, H);
     }
-    return check_launch("add_rmsnorm");
 }
 
 // delta_dtype / w_dtype / out_dtype: 0 = float32, 1 = bfloat16.
@@ -229,6 +286,16 @@ extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, l
     FD_REQUIRE(H > 0, -2, "add_rmsnorm: bad width %d", H);
     FD_REQUIRE(delta == nullptr || n_parts >= 1, -2, "add_rmsnorm: n_parts=%d", n_parts);
     const size_t ps = (size_t)part_stride;
+    if (out_dtype == 1 && (delta == nullptr || (delta_dtype == 1 && n_parts == 1)) && H % 8 == 0 && H <= 8192 &&
+        (uintptr_t)resid % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)weight % 16 == 0 &&
+        (uintptr_t)delta % 16 == 0) {
+        const int threads = ((H / 8 + 31) / 32) * 32;
+        if (w_dtype == 0)
+            return launch("add_rmsnorm", add_rmsnorm_row_kernel<float>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+                          (const bf16*)delta, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
+        return launch("add_rmsnorm", add_rmsnorm_row_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+                      (const bf16*)delta, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
+    }
     if (delta_dtype == 0 && out_dtype == 0)
         return launch_norm<float, float>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);
     if (delta_dtype == 1 && out_dtype == 1)

@@ -107,15 +107,31 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
     // this warp takes chunks wk, wk + WK, ...: at any moment the WK warps of a row tile read
-    // neighbouring 64-byte pieces of the same rows
+    // neighbouring 64-byte pieces of the same rows.  The first batch of W is fetched before the
+    // wait on the previous kernel: weights depend on nothing an earlier kernel wrote.
+    pdl_launch_dependents();
     int kc = wk;
-    for (; kc + (UNROLL - 1) * WK < n_chunks; kc += UNROLL * WK) {
-        uint4 a[UNROLL], b[UNROLL], xv[UNROLL][NT];
+    const bool first_full = kc + (UNROLL - 1) * WK < n_chunks;
+    uint4 a[UNROLL], b[UNROLL];
+    if (first_full) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             a[u] = ldg_stream(w0 + (kc + u * WK) * 32);
             b[u] = ldg_stream(w1 + (kc + u * WK) * 32);
         }
+    }
+    pdl_wait();
+    bool have = first_full;
+    for (; kc + (UNROLL - 1) * WK < n_chunks; kc += UNROLL * WK) {
+        uint4 xv[UNROLL][NT];
+        if (!have) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                a[u] = ldg_stream(w0 + (kc + u * WK) * 32);
+                b[u] = ldg_stream(w1 + (kc + u * WK) * 32);
+            }
+        }
+        have = false;
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
@@ -285,25 +301,10 @@ template <int NT, int WK, int UNROLL>
 static int launch_gemv(const GemvParams& p, const RopeArgs& ra, cudaStream_t stream) {
     constexpr int rows = 16 * (GV_WARPS / WK);
     dim3 grid((p.N + rows - 1) / rows, p.n_splits);
-    if (p.n_splits > 1 && p.mode != 0) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(GV_THREADS);
-        cfg.dynamicSmemBytes = 0;
-        cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 1;
-        attr[0].val.clusterDim.y = p.n_splits;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<NT, WK, UNROLL, true>, p, ra);
-        if (e != cudaSuccess) return fail(-100, "gemv_mma: cluster launch failed: %s", cudaGetErrorString(e));
-        return 0;
-    }
-    gemv_mma_kernel<NT, WK, UNROLL, false><<<grid, GV_THREADS, 0, stream>>>(p, ra);
-    return check_launch("gemv_mma");
+    if (p.n_splits > 1 && p.mode != 0)
+        return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, true>, grid, dim3(GV_THREADS), 0, stream,
+                      dim3(1, p.n_splits, 1), p, ra);
+    return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, false>, grid, dim3(GV_THREADS), 0, stream, dim3(1, 1, 1), p, ra);
 }
 
 // Measured on B200 (graph-timed, weights beyond L2): wide matrices stream best with 32 rows
@@ -344,7 +345,9 @@ extern "C" int fd_gemv_splits(int M, int N, int K, int target_ctas, int allow_sp
     const int row_blocks = (N + rows - 1) / rows;
     int want = (target_ctas + row_blocks / 2) / row_blocks;
     const int chunks = K / 32;
-    if (want > chunks / 8) want = chunks / 8;             // a split keeps at least 8 chunks (256 k)
+    // A split across CTAs costs a cluster launch and two cluster barriers (about 3 us measured on
+    // B200): worth it only while every warp of a CTA still walks 8 or more chunks.
+    if (want > chunks / (8 * 8)) want = chunks / (8 * 8);
     if (want > 8) want = 8;                               // the most CTAs a portable cluster holds
     if (want < 1) want = 1;
     const int per = ((chunks + want - 1) / want) * 32;    // k per split, multiple of 32

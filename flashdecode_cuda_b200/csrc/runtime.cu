@@ -12,6 +12,8 @@ extern "C" const char* fd_last_error() { return g_error; }
 
 namespace fd {
 
+int g_pdl = 0;
+
 int fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -43,4 +45,10 @@ extern "C" int fd_sm_count() {
     if (cudaGetDevice(&dev) != cudaSuccess) return fd::fail(-1, "no CUDA device");
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     return n;
+}
+
+// Turn programmatic dependent launch on (1) or off (0, the default) for later launches.
+extern "C" int fd_set_pdl(int on) {
+    fd::g_pdl = on ? 1 : 0;
+    return 0;
 }

@@ -39,6 +39,8 @@ sample_partial_kernel(const float* __restrict__ logits, int V, const float* __re
                       const long long* __restrict__ request, const int* __restrict__ step,
                       unsigned long long seed, float* __restrict__ part_v, int* __restrict__ part_i,
                       int* __restrict__ out, int n_chunks) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.y, chunk = blockIdx.x;
     const float* x = logits + (size_t)row * V;
     const float temp = temperature ? temperature[row] : 0.f;
@@ -102,6 +104,8 @@ sample_partial_kernel(const float* __restrict__ logits, int V, const float* __re
 // One warp per row merges the chunks' winners.
 __global__ void sample_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
                                     int n_chunks, int* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, lane = threadIdx.x;
     float bv = -INFINITY;
     int bi = 0x7fffffff;

@@ -29,8 +29,11 @@ GEMV_MAX_ROWS = 16
 
 
 def fused_prompt_gemm(M: int, N: int, Kd: int) -> bool:
-    """Whether a prompt-step product with a fused epilogue goes to the tcgen05 kernel."""
-    return PROMPT_GEMM != "cublas" and K.gemm_tc_supported(M, N, Kd)
+    """Whether a product with a fused epilogue goes to the tcgen05 kernel: from one full
+    128-row tile on (between GEMV_MAX_ROWS and 128 rows its tiles would be mostly padding)."""
+    if PROMPT_GEMM == "cublas" or not K.gemm_tc_supported(M, N, Kd):
+        return False
+    return PROMPT_GEMM == "tcgen05" or M >= 128
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
