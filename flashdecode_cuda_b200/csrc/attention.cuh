@@ -19,6 +19,7 @@ struct AttnParams {
     const int* row_q_len;      // new tokens of the row in this step
     const int* row_ctx_len;    // tokens of the row cached before this step
     int* status;
+    int* counters;             // [rows, n_kv] arrival counts for the in-kernel merge of the splits (all zero between launches), or null
     int max_blocks, num_blocks, block_size;
     int n_q, n_kv, G, d;
     int QT, n_splits, split_len, window;

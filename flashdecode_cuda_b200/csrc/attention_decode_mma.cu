@@ -2,7 +2,7 @@
 // on the tensor cores: split-KV flash-decoding.
 //
 // A CTA serves one (sequence, KV head, split of the keys); its 4 warps take
-// 16-key tiles of the split round-robin, each with its own double-buffered
+// 16-key tiles of the split round-robin, each with its own three-stage
 // cp.async pipeline into swizzled shared memory and its own online-softmax
 // state, so the main loop has no block-wide barrier.  All G query heads of the
 // KV head form the M = 16 rows of the tile (rows >= G are zero), so every key
@@ -26,7 +26,7 @@ namespace fd {
 constexpr int DM_WARPS = 4;
 constexpr int DM_THREADS = DM_WARPS * 32;
 constexpr int DM_TILE = 16;       // keys per warp tile
-constexpr int DM_STAGES = 2;
+constexpr int DM_STAGES = 3;     // tiles of a warp under way or in use: two loads always in flight
 
 template <int D>
 __global__ void __launch_bounds__(DM_THREADS)
@@ -38,10 +38,16 @@ attn_decode_mma_kernel(const AttnParams p) {
     pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int slot = p.row_slot[b];
-    if (slot < 0) return;                       // padding row; the merge kernel writes its zeros
-    const int ctx = p.row_ctx_len[b];
     const int tok = p.row_q_start[b];
     const int G = p.G;
+    if (slot < 0) {
+        // padding row: zeros, written here when no merge kernel follows
+        if (p.counters != nullptr && split == 0)
+            for (int e = threadIdx.x; e < G * D; e += DM_THREADS)
+                static_cast<__nv_bfloat16*>(p.out)[((size_t)tok * p.n_q + kvh * G) * D + e] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int ctx = p.row_ctx_len[b];
     int lo = p.window > 0 ? max(0, ctx - p.window + 1) : 0;
     int hi = ctx + 1;                           // the new token's own key is already in the cache
     if (p.n_splits > 1) {
@@ -85,6 +91,8 @@ attn_decode_mma_kernel(const AttnParams p) {
 
     unsigned char* my = kv_s + warp * WARP_BYTES;
     const int bs = p.block_size;
+    const int bs_shift = (bs & (bs - 1)) == 0 ? __ffs(bs) - 1 : -1;     // powers of two: shift and mask
+    const bool tile_in_block = bs_shift >= 4;                           // a 16-key tile then lies in one block
     const int first_tile = lo / DM_TILE;
     const int n_tiles = hi > lo ? (hi - 1) / DM_TILE - first_tile + 1 : 0;
 
@@ -93,6 +101,11 @@ attn_decode_mma_kernel(const AttnParams p) {
         const int t0 = (first_tile + j) * DM_TILE;
         unsigned char* ks = my + stage * 2 * TILE_BYTES;
         unsigned char* vs = ks + TILE_BYTES;
+        int tile_blk = -1, tile_off = 0;
+        if (tile_in_block) {
+            tile_blk = p.block_table[(size_t)slot * p.max_blocks + (t0 >> bs_shift)];
+            tile_off = t0 & (bs - 1);
+        }
 #pragma unroll
         for (int i = 0; i < DM_TILE * CPR / 32; ++i) {
             const int c = i * 32 + lane;
@@ -102,11 +115,14 @@ attn_decode_mma_kernel(const AttnParams p) {
             const __nv_bfloat16* vsrc = vp;
             int bytes = 0;
             if (t >= lo && t < hi) {
-                const int blk = p.block_table[(size_t)slot * p.max_blocks + t / bs];
+                int blk, in_blk;
+                if (tile_in_block) { blk = tile_blk; in_blk = tile_off + r; }
+                else if (bs_shift >= 0) { blk = p.block_table[(size_t)slot * p.max_blocks + (t >> bs_shift)]; in_blk = t & (bs - 1); }
+                else { const int col = t / bs; blk = p.block_table[(size_t)slot * p.max_blocks + col]; in_blk = t - col * bs; }
                 if (blk < 0 || blk >= p.num_blocks) {
                     set_status(p.status, STATUS_BAD_BLOCK);
                 } else {
-                    const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + (t % bs)) * D + cc * 8;
+                    const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + in_blk) * D + cc * 8;
                     ksrc = kp + off;
                     vsrc = vp + off;
                     bytes = 16;
@@ -120,17 +136,20 @@ attn_decode_mma_kernel(const AttnParams p) {
 
     int n_mine = 0;
     for (int j = warp; j < n_tiles; j += DM_WARPS) ++n_mine;
-    if (n_mine > 0) issue(warp, 0);
+    // prologue: the first DM_STAGES - 1 tiles (an empty group keeps the count uniform)
+#pragma unroll
+    for (int st = 0; st < DM_STAGES - 1; ++st) {
+        if (st < n_mine) issue(warp + st * DM_WARPS, st);
+        else cp_async_commit();
+    }
     for (int i = 0; i < n_mine; ++i) {
         const int j = warp + i * DM_WARPS;
-        if (i + 1 < n_mine) {
-            issue(j + DM_WARPS, (i + 1) & 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        cp_async_wait<DM_STAGES - 2>();       // tile i has landed
         __syncwarp();
-        const unsigned char* ks = my + (i & 1) * 2 * TILE_BYTES;
+        // refill the stage that iteration i - 1 finished with
+        if (i + DM_STAGES - 1 < n_mine) issue(j + (DM_STAGES - 1) * DM_WARPS, (i + DM_STAGES - 1) % DM_STAGES);
+        else cp_async_commit();
+        const unsigned char* ks = my + (i % DM_STAGES) * 2 * TILE_BYTES;
         const unsigned char* vs = ks + TILE_BYTES;
 
         // S = Q K^T for 16 keys: two n-tiles of 8 keys
@@ -181,6 +200,7 @@ attn_decode_mma_kernel(const AttnParams p) {
         const uint32_t pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
         const uint32_t pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
         // O = O * alpha + P V
+        const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
         {
             const int mi = lane >> 3;
             const int r = (mi & 1) * 8 + (lane & 7);             // key row
@@ -190,8 +210,10 @@ attn_decode_mma_kernel(const AttnParams p) {
                 ldmatrix_x4_trans(smem_u32(vs + swz<D>(r, np * 2 + (mi >> 1))), b0, b1, b2, b3);
                 float* oa = o[np * 2];
                 float* ob = o[np * 2 + 1];
-                oa[0] *= alpha[0]; oa[1] *= alpha[0]; oa[2] *= alpha[1]; oa[3] *= alpha[1];
-                ob[0] *= alpha[0]; ob[1] *= alpha[0]; ob[2] *= alpha[1]; ob[3] *= alpha[1];
+                if (rescale) {       // most tiles leave every running maximum as it was
+                    oa[0] *= alpha[0]; oa[1] *= alpha[0]; oa[2] *= alpha[1]; oa[3] *= alpha[1];
+                    ob[0] *= alpha[0]; ob[1] *= alpha[0]; ob[2] *= alpha[1]; ob[3] *= alpha[1];
+                }
                 mma_bf16(oa, pa0, pa1, pa2, pa3, b0, b1);
                 mma_bf16(ob, pa0, pa1, pa2, pa3, b2, b3);
             }
@@ -199,6 +221,7 @@ attn_decode_mma_kernel(const AttnParams p) {
         __syncwarp();      // every lane is done with this stage before it is refilled
     }
 
+    cp_async_wait<0>();
     // per-warp results to shared memory: O as float [16][D] in the warp's own staging area
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -239,10 +262,62 @@ attn_decode_mma_kernel(const AttnParams p) {
         if (p.n_splits > 1) {
             const size_t pi = row * p.n_splits + split;
             p.part_acc[pi * D + j] = a;
-            if (j == 0) { p.part_m[pi] = m * LN2; p.part_l[pi] = l; }   // natural-log units for the merge kernel
+            if (j == 0) { p.part_m[pi] = m * LN2; p.part_l[pi] = l; }   // natural-log units for the merge
         } else {
             static_cast<__nv_bfloat16*>(p.out)[row * D + j] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
         }
+    }
+    if (p.n_splits == 1 || p.counters == nullptr) return;
+
+    // The CTA that finishes last for this (sequence, KV head) merges the splits: no CTA waits for
+    // another.  Its partial results are made visible device-wide before it announces itself.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* cnt = p.counters + (size_t)b * p.n_kv + kvh;
+        const int old = atomicAdd(cnt, 1);
+        is_last = old == p.n_splits - 1;
+        if (is_last) *cnt = 0;                       // ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // weights e^(m_s - m) / l of every (head, split), one warp per head; the staging area is free now
+    float* wgt = reinterpret_cast<float*>(kv_s);     // [G][n_splits]
+    const int ns = p.n_splits;
+    for (int r = warp; r < G; r += DM_WARPS) {
+        const size_t base = ((size_t)tok * p.n_q + kvh * G + r) * ns;
+        float m = -INFINITY;
+        for (int s = lane; s < ns; s += 32)
+            if (__ldcg(p.part_l + base + s) > 0.f) m = fmaxf(m, __ldcg(p.part_m + base + s));
+        m = warp_max(m);
+        float lsum = 0.f;
+        for (int s = lane; s < ns; s += 32) {
+            const float ls = __ldcg(p.part_l + base + s);
+            const float w = ls > 0.f ? expf(__ldcg(p.part_m + base + s) - m) : 0.f;
+            wgt[r * ns + s] = w;
+            lsum += ls * w;
+        }
+        lsum = warp_sum(lsum);
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        for (int s = lane; s < ns; s += 32) wgt[r * ns + s] *= inv;
+    }
+    __syncthreads();
+    for (int e = tid; e < G * D; e += DM_THREADS) {
+        const int r = e / D, j = e - r * D;
+        const size_t row = (size_t)tok * p.n_q + kvh * G + r;
+        const float* pa = p.part_acc + row * ns * D + j;
+        const float* w = wgt + r * ns;
+        float a = 0.f;
+        int s = 0;
+        for (; s + 4 <= ns; s += 4) {
+            const float a0 = __ldcg(pa + (size_t)(s + 0) * D), a1 = __ldcg(pa + (size_t)(s + 1) * D);
+            const float a2 = __ldcg(pa + (size_t)(s + 2) * D), a3 = __ldcg(pa + (size_t)(s + 3) * D);
+            a = fmaf(a0, w[s], a); a = fmaf(a1, w[s + 1], a); a = fmaf(a2, w[s + 2], a); a = fmaf(a3, w[s + 3], a);
+        }
+        for (; s < ns; ++s) a = fmaf(__ldcg(pa + (size_t)s * D), w[s], a);
+        static_cast<__nv_bfloat16*>(p.out)[row * D + j] = __float2bfloat16_rn(a);
     }
 }
 
@@ -263,6 +338,8 @@ static int launch_dm(const AttnParams& p, int n_rows, cudaStream_t stream) {
 
 int launch_attn_decode_mma(const AttnParams& p, int n_rows, cudaStream_t stream) {
     if (p.G > 16) return 1;
+    // the in-kernel merge keeps G * n_splits weights in the 64 KB (32 KB at D = 64) staging area
+    if (p.counters != nullptr && (size_t)p.G * p.n_splits * sizeof(float) > 16 * 1024) return 1;
     if (p.d == 128) return launch_dm<128>(p, n_rows, stream);
     if (p.d == 64) return launch_dm<64>(p, n_rows, stream);
     return 1;

@@ -345,7 +345,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
                           const int* tok_row, const int* row_slot, const int* row_q_start,
                           const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
                           int max_q_len, int n_q, int n_kv, int d, float scale, int window,
-                          int n_splits, int split_len, float* scratch, int* status, int use_mma,
+                          int n_splits, int split_len, float* scratch, int* counters, int* status, int use_mma,
                           cudaStream_t stream) {
     if (n_rows == 0 || T == 0) return 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
@@ -372,6 +372,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     p.part_l = scratch ? scratch + n_part * d + n_part : nullptr;
     p.block_table = block_table; p.row_slot = row_slot; p.row_q_start = row_q_start;
     p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len; p.status = status;
+    p.counters = nullptr;
     p.max_blocks = max_blocks; p.num_blocks = num_blocks; p.block_size = block_size;
     p.n_q = n_q; p.n_kv = n_kv; p.G = G; p.d = d;
     int qt = fd_attn_simt_qt(G);
@@ -379,7 +380,12 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     p.QT = qt; p.n_splits = n_splits; p.split_len = split_len; p.window = window; p.scale = scale;
 
     int rc = 1;
-    if (use_mma && dtype == 1 && max_q_len == 1) rc = launch_attn_decode_mma(p, n_rows, stream);
+    if (use_mma && dtype == 1 && max_q_len == 1) {
+        p.counters = n_splits > 1 ? counters : nullptr;     // given: the kernel merges its own splits
+        rc = launch_attn_decode_mma(p, n_rows, stream);
+        if (rc == 0 && p.counters != nullptr) return 0;
+        p.counters = nullptr;
+    }
     else if (use_mma && dtype == 1) rc = launch_attn_prefill_mma(p, n_rows, max_q_len, stream);
     if (rc == 1)
         rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
@@ -405,18 +411,21 @@ extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* 
                                  cudaStream_t stream) {
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
-                          window, n_splits, split_len, scratch, status, 0, stream);
+                          window, n_splits, split_len, scratch, nullptr, status, 0, stream);
 }
 
-// The fastest kernel that takes the sizes: tensor cores where possible.
+// The fastest kernel that takes the sizes: tensor cores where possible.  `counters`
+// (optional): n_rows * n_kv ints, all zero, which the decode kernel uses to let the last CTA of
+// a (sequence, KV head) merge the splits itself (it leaves them zero again); without them the
+// separate merge kernel runs.
 extern "C" int fd_attention(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
                             const int* block_table, int max_blocks, int num_blocks, int block_size,
                             const int* tok_row, const int* row_slot, const int* row_q_start,
                             const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
                             int max_q_len, int n_q, int n_kv, int d, float scale, int window,
-                            int n_splits, int split_len, float* scratch, int* status,
+                            int n_splits, int split_len, float* scratch, int* counters, int* status,
                             cudaStream_t stream) {
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
-                          window, n_splits, split_len, scratch, status, 1, stream);
+                          window, n_splits, split_len, scratch, counters, status, 1, stream);
 }

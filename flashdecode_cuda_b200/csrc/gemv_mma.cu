@@ -107,31 +107,17 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
     for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
     // this warp takes chunks wk, wk + WK, ...: at any moment the WK warps of a row tile read
-    // neighbouring 64-byte pieces of the same rows.  The first batch of W is fetched before the
-    // wait on the previous kernel: weights depend on nothing an earlier kernel wrote.
+    // neighbouring 64-byte pieces of the same rows
     pdl_launch_dependents();
+    pdl_wait();
     int kc = wk;
-    const bool first_full = kc + (UNROLL - 1) * WK < n_chunks;
-    uint4 a[UNROLL], b[UNROLL];
-    if (first_full) {
+    for (; kc + (UNROLL - 1) * WK < n_chunks; kc += UNROLL * WK) {
+        uint4 a[UNROLL], b[UNROLL], xv[UNROLL][NT];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             a[u] = ldg_stream(w0 + (kc + u * WK) * 32);
             b[u] = ldg_stream(w1 + (kc + u * WK) * 32);
         }
-    }
-    pdl_wait();
-    bool have = first_full;
-    for (; kc + (UNROLL - 1) * WK < n_chunks; kc += UNROLL * WK) {
-        uint4 xv[UNROLL][NT];
-        if (!have) {
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                a[u] = ldg_stream(w0 + (kc + u * WK) * 32);
-                b[u] = ldg_stream(w1 + (kc + u * WK) * 32);
-            }
-        }
-        have = false;
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
 #pragma unroll

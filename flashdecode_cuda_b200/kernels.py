@@ -87,7 +87,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
         "fd_attn_simt_qt": [I],
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
-        "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
+        "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
     }
     for name, args in sigs.items():
@@ -311,6 +311,16 @@ def attention_scratch_floats(n_tokens: int, n_q: int, head_dim: int, n_splits: i
     return int(lib().fd_attn_scratch_floats(n_tokens, n_q, head_dim, n_splits))
 
 
+_attn_counters = {}      # per device: zeroed ints the decode kernel counts arriving splits in (kept alive for good)
+
+
+def _counters(device, n: int) -> torch.Tensor:
+    bufs = _attn_counters.setdefault(device, [])
+    if not bufs or bufs[-1].numel() < n:
+        bufs.append(torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device))
+    return bufs[-1]
+
+
 def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
                row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
                scratch, status) -> None:
@@ -320,12 +330,15 @@ def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, 
     if n_splits > 1:
         assert scratch is not None and scratch.dtype == torch.float32
         assert scratch.numel() >= attention_scratch_floats(T, n_q, head_dim, n_splits)
-    _check(getattr(lib(), fn_name)(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype),
-                                   _ptr(block_table), block_table.shape[1], num_blocks, block_size,
-                                   _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len),
-                                   _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale),
-                                   int(window), n_splits, split_len, _ptr(scratch), _ptr(status), _stream()),
-           kernels=2 if n_splits > 1 else 1)
+    args = [_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _dt(q.dtype), _ptr(block_table), block_table.shape[1],
+            num_blocks, block_size, _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len),
+            _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), n_splits,
+            split_len, _ptr(scratch)]
+    if fn_name == "fd_attention":
+        fused = n_splits > 1 and max_q_len == 1 and q.dtype == torch.bfloat16
+        args.append(_ptr(_counters(q.device, n_rows * n_kv)) if fused else None)
+    args += [_ptr(status), _stream()]
+    _check(getattr(lib(), fn_name)(*args), kernels=2 if n_splits > 1 else 1)
 
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
