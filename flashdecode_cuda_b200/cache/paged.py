@@ -79,6 +79,10 @@ class KVGroup:
         self.table_host = np.full((max_slots, max_blocks_per_seq), -1, dtype=np.int32)
         self.table = torch.full((max_slots, max_blocks_per_seq), -1, dtype=torch.int32, device=device)
         self._pending: Dict[Tuple[int, int], int] = {}     # (slot, column) -> block, not yet on the device
+        self._ring: List[Optional[torch.Tensor]] = [None] * 4          # pinned staging buffers
+        self._ring_events: List[Optional[torch.cuda.Event]] = [None] * 4
+        self._ring_i = 0
+        self._dev_updates: Optional[torch.Tensor] = None
 
     def k_pool(self, layer: int) -> torch.Tensor:
         return self.pool[layer, 0]
@@ -91,18 +95,37 @@ class KVGroup:
         self._pending[(slot, col)] = block       # a later value for the same entry replaces the earlier
 
     def sync(self) -> None:
-        """Bring the device table up to date with one small copy."""
+        """Bring the device table up to date with one small copy: [indices | values] from a ring
+        of pinned buffers (a buffer is reused only after the copy that read it has completed)."""
         if not self._pending:
             return
+        n = len(self._pending)
         width = self.max_blocks_per_seq
-        idx = torch.tensor([s * width + c for s, c in self._pending], dtype=torch.int64)
-        val = torch.tensor(list(self._pending.values()), dtype=torch.int32)
+        flat = np.empty(2 * n, dtype=np.int32)
+        flat[:n] = [s * width + c for s, c in self._pending]
+        flat[n:] = list(self._pending.values())
         self._pending.clear()
         dev = self.table.device
-        if dev.type == "cuda":
-            idx = idx.pin_memory().to(dev, non_blocking=True)
-            val = val.pin_memory().to(dev, non_blocking=True)
-        self.table.view(-1).index_copy_(0, idx, val)
+        if dev.type != "cuda":
+            t = torch.from_numpy(flat)
+            self.table.view(-1).index_copy_(0, t[:n].long(), t[n:])
+            return
+        i = self._ring_i
+        self._ring_i = (i + 1) % len(self._ring)
+        if self._ring_events[i] is not None:
+            self._ring_events[i].synchronize()
+        buf = self._ring[i]
+        if buf is None or buf.numel() < 2 * n:
+            buf = torch.empty(max(2 * n, 512), dtype=torch.int32).pin_memory()
+            self._ring[i] = buf
+        buf[:2 * n].numpy()[:] = flat
+        if self._dev_updates is None or self._dev_updates.numel() < 2 * n:
+            self._dev_updates = torch.empty(max(2 * n, 512), dtype=torch.int32, device=dev)
+        self._dev_updates[:2 * n].copy_(buf[:2 * n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._ring_events[i] = ev
+        self.table.view(-1).index_copy_(0, self._dev_updates[:n].long(), self._dev_updates[n:2 * n])
 
     def bytes_per_token(self) -> int:
         s = self.spec

@@ -82,8 +82,9 @@ class Engine(Backend):
         temps = [r.temperature for r in requests]
         rids = [r.request_id for r in requests]
         if self.use_graphs and all(len(t) == 1 for t in tokens):
-            toks = self._decoder().run(slots, [t[0] for t in tokens], temps, rids, steps, self.seed)
-            return toks[:len(slots)].tolist()
+            dec = self._decoder()
+            dec.run(slots, [t[0] for t in tokens], temps, rids, steps, self.seed)
+            return dec.read_tokens(len(slots))
         logits = self.model.step(self.cache, slots, tokens, "last")
         toks = self.sampler.sample(logits, temps, rids, steps, self.seed)
         return toks.tolist()

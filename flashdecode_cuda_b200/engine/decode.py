@@ -45,6 +45,9 @@ class _Graph:
         self.temp = self.req = self.step = None
         self.launches = 0
         self.sample_scratch = None
+        self.n_rows_real = 0
+        self.host: Optional[np.ndarray] = None       # the step's index array; only a few slices change per step
+        self.meta: Optional[torch.Tensor] = None     # its device copy (fixed address)
 
 
 class GraphDecoder:
@@ -59,6 +62,7 @@ class GraphDecoder:
         self.last: Optional[_Graph] = None
         self.last_n = 0
         self.launches_per_step = 0
+        self._host_out: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------
     def _key(self, n: int, longest: int, greedy: bool, seed: int) -> Tuple:
@@ -77,10 +81,34 @@ class GraphDecoder:
         else:
             K.sample(logits, g.sampled, g.temp, g.req, g.step, key[3], scratch=g.sample_scratch)
 
+    def _refill(self, g: _Graph, key: Tuple, slots: Sequence[int], tokens: Sequence[int]) -> None:
+        """Re-upload the index array of a captured graph for a new step: the batch-shape parts
+        (rows of tokens, counts, wanted rows) never change; tokens, slots and lengths do."""
+        B, n = key[0], len(slots)
+        cache = self.cache
+        lens = [cache.length(s) for s in slots]
+        if max(lens) + 1 > cache.max_len:
+            raise ValueError(f"a sequence would grow beyond the cache's longest sequence {cache.max_len}")
+        toks = np.asarray(tokens, dtype=np.int64)
+        if toks.min() < 0 or toks.max() >= self.model.vocab_size:
+            raise ValueError(f"token ids must lie in [0, {self.model.vocab_size})")
+        h = g.host
+        h[0:n] = toks
+        h[2 * B:2 * B + n] = lens               # positions of the new tokens
+        h[3 * B:3 * B + n] = slots
+        h[3 * B + n:4 * B] = -1
+        h[6 * B:6 * B + n] = lens               # tokens cached before the step
+        self.model._staging.upload(h, g.meta)
+
     def _graph_for(self, key: Tuple, slots, tokens) -> Tuple[_Graph, StepContext]:
         g = self.graphs.get(key)
+        if g is not None and len(slots) == g.n_rows_real:
+            self._refill(g, key, slots, tokens)
+            return g, g.ctx
         if g is not None:
-            return g, self._prepare(g, key, slots, tokens)
+            ctx = self._prepare(g, key, slots, tokens)      # same bucket, another number of real rows
+            g.host, g.n_rows_real = self.model.last_meta_host.copy(), len(slots)
+            return g, ctx
         B = key[0]
         dev = self.model.device
         g = _Graph(Workspace(dev))
@@ -91,6 +119,8 @@ class GraphDecoder:
         g.sample_scratch = torch.zeros(max(1, K.sample_scratch_words(B, self.model.vocab_size)),
                                        dtype=torch.int32, device=dev)
         ctx = self._prepare(g, key, slots, tokens)
+        g.host, g.n_rows_real = self.model.last_meta_host.copy(), len(slots)
+        g.meta = g.ws.get("step_meta", (g.host.size,), torch.int32)
         # one eager run: it allocates the workspace and writes this step's keys
         # and values; the captured replay below rewrites the same values
         self._body(g, ctx, key)
@@ -139,3 +169,12 @@ class GraphDecoder:
         self.last, self.last_n = g, n
         self.launches_per_step = g.launches
         return g.sampled
+
+    def read_tokens(self, n: int) -> List[int]:
+        """The first ``n`` tokens of the last step as host integers (one copy into pinned memory)."""
+        src = self.last.sampled
+        if self._host_out is None or self._host_out.numel() < src.numel():
+            self._host_out = torch.empty(max(src.numel(), 256), dtype=torch.int32).pin_memory()
+        self._host_out[:src.numel()].copy_(src, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._host_out[:n].tolist()

@@ -130,6 +130,7 @@ class Model:
         self.ws: Optional[Workspace] = None
         self._staging = _Staging()
         self.trace: Optional[Dict[str, torch.Tensor]] = None    # set to {} to record per-layer activations
+        self.last_meta_host: Optional[np.ndarray] = None        # the index array of the last prepared step
         self.bound = False
 
     # ------------------------------------------------------------------ build
@@ -340,6 +341,7 @@ class Model:
             np.asarray(wanted, dtype=np.int32)])
         ws = ws or self.ws
         meta = ws.get("step_meta", (host.size,), torch.int32)
+        self.last_meta_host = host
         self._staging.upload(host, meta)
         o = 0
 
