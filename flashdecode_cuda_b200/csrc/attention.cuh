@@ -31,5 +31,7 @@ struct AttnParams {
 int launch_attn_decode_mma(const AttnParams& p, int n_rows, cudaStream_t stream);
 // prompt steps (several new tokens per row) on the tensor cores; same return convention
 int launch_attn_prefill_mma(const AttnParams& p, int n_rows, int max_q_len, cudaStream_t stream);
+// the same on the tcgen05 tensor cores (head size 128, block sizes 8..128 that divide 128)
+int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_q_len, cudaStream_t stream);
 
 }  // namespace fd

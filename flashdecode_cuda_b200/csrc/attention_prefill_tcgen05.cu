@@ -1,0 +1,486 @@
+// Prompt attention on the 5th-generation tensor cores (head size 128, bfloat16):
+// causal, grouped-query, paged, variable lengths, optional window, continuing a
+// cached prefix.  A CTA takes 128 consecutive query tokens of one sequence and
+// one query head and walks the keys in tiles of 64:
+//
+//   S[128 q, 64 keys] = Q K^T      tcgen05.mma, both operands K-major in shared memory,
+//                                  accumulator S in tensor memory (64 columns)
+//   softmax                        4 warps, one thread per query row: tcgen05.ld of its S row,
+//                                  running max / sum in float (base 2), P written to shared
+//                                  memory as bfloat16 in the 128-byte-swizzled K-major layout
+//   O[128 q, 128 d] += P V         tcgen05.mma with V as an MN-major operand (V rows are keys,
+//                                  the head dimension is contiguous), accumulator O in tensor
+//                                  memory (128 more columns), rescaled in place when a row's
+//                                  maximum moved
+//
+// Keys and values come straight from the paged pools by TMA: one 2-D box of
+// (block_size keys x 64 dims) per cache block and half head, placed so that a
+// tile of 64 keys forms the canonical swizzled layout.  Roles: warp 0 issues
+// TMA, warp 1 issues MMAs and owns the tensor-memory allocation, warps 2-5 do
+// the softmax and the epilogue.  Every mbarrier wait is bounded in time; a wait
+// that runs out sets a status bit and the CTA winds down (see gemm_tcgen05.cu).
+#include <cuda.h>
+#include <math.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "attention.cuh"
+
+namespace fd {
+
+constexpr int TA_D = 128;                 // head size
+constexpr int TA_BM = 128;                // queries per CTA
+constexpr int TA_BN = 64;                 // keys per tile
+constexpr int TA_STAGES = 2;              // key/value tiles in flight
+constexpr int TA_THREADS = 192;
+constexpr int TA_QSLAB = TA_BM * 128;     // bytes of a [128 queries][64 bf16] slab (Q: two of them; P: one)
+constexpr int TA_KSLAB = TA_BN * 128;     // bytes of a [64 keys][64 bf16] slab (K and V: two each)
+constexpr int TA_QTILE = 2 * TA_QSLAB;    // Q [128][128]
+constexpr int TA_PTILE = TA_QSLAB;        // P [128][64]
+constexpr int TA_KTILE = 2 * TA_KSLAB;    // K or V [64][128]
+// 112 KB + barriers: two CTAs share an SM (and its 512 tensor-memory columns, 256 each), so one
+// CTA's softmax runs under the other's matrix products
+constexpr int TA_SMEM = TA_QTILE + TA_PTILE + TA_STAGES * 2 * TA_KTILE + 128;
+constexpr unsigned long long TA_WAIT_NS = 200ull * 1000 * 1000;
+
+__device__ __forceinline__ uint32_t ta_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long ta_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool ta_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    unsigned long long t0 = 0;
+    for (uint32_t spins = 0;; ++spins) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spins & 63) != 63) continue;                    // the clock and the flag only now and then
+        if (*abort_flag) return false;
+        if (t0 == 0) t0 = ta_ns();
+        else if (ta_ns() - t0 > TA_WAIT_NS) {
+            *abort_flag = 1;
+            set_status(status, STATUS_WAIT_TIMEOUT);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void ta_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void ta_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ta_tma(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void ta_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void ta_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void ta_ld32(uint32_t taddr, uint32_t v[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void ta_st32(uint32_t taddr, const uint32_t v[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+
+// K-major operand, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
+// 2^x by the special function unit (two units in the last place; 2^-inf = 0)
+__device__ __forceinline__ float ta_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint64_t ta_desc_k(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (rows are the contraction index, 64 contiguous elements of the N side per
+// 128-byte row, 128-byte swizzle): slabs of 64 N-elements `slab_bytes` apart (leading offset),
+// 8-row groups along K 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t ta_desc_mn(uint32_t addr, uint32_t slab_bytes) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(slab_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+__global__ void __launch_bounds__(TA_THREADS, 2)
+attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+    extern __shared__ __align__(1024) unsigned char ta_raw[];
+    unsigned char* q_s = ta_raw;                             // [2 slabs][128 q][64 d]
+    unsigned char* p_s = q_s + TA_QTILE;                     // [128 q][64 keys]
+    unsigned char* kv_s = p_s + TA_PTILE;                    // per stage: K [2 slabs][64 keys][64 d], V the same
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + TA_STAGES * 2 * TA_KTILE);
+    // bars: [0] q_full, kv_full[S], kv_empty[S], s_full[2], p_ready, o_done
+    uint64_t* kv_full = bars + 1;
+    uint64_t* kv_empty = kv_full + TA_STAGES;
+    uint64_t* s_full = kv_empty + TA_STAGES;
+    uint64_t* p_ready = s_full + 2;
+    uint64_t* o_done = p_ready + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // long tiles first (see attention_prefill_mma.cu)
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int slot = p.row_slot[b];
+    const int q_len = slot >= 0 ? p.row_q_len[b] : 0;
+    if (tile * TA_BM >= q_len) return;                       // uniform for the CTA; nothing allocated yet
+    if ((ta_saddr(ta_raw) & 1023u) != 0) {                   // the swizzled tiles need a 1024-byte-aligned base
+        if (threadIdx.x == 0) set_status(p.status, STATUS_WAIT_TIMEOUT);
+        return;
+    }
+    const int ctx = p.row_ctx_len[b];
+    const int tok0 = p.row_q_start[b] + tile * TA_BM;
+    const int nq = min(TA_BM, q_len - tile * TA_BM);
+    const int kvh = h / p.G;
+    const int p_first = ctx + tile * TA_BM;
+    const int hi = p_first + nq;
+    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int bs = p.block_size;
+    const int t_begin = (lo / TA_BN) * TA_BN;
+    const int n_tiles = (hi - t_begin + TA_BN - 1) / TA_BN;
+
+    if (threadIdx.x == 0) {
+        abort_flag[0] = 0;
+        abort_flag[1] = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&bars[0])) : "memory");
+        for (int s = 0; s < TA_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&kv_full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&kv_empty[s])) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&s_full[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&s_full[1])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(ta_saddr(p_ready)) : "memory");   // every softmax thread arrives
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(o_done)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ta_saddr(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;       // columns 0..63 and 64..127: two S tiles, 128..255: O
+
+    if (warp == 0) {
+        // ---- TMA producer: lane 0 issues the copies; the warp's lanes fetch the block numbers of the
+        // next 32 copies together, one chunk ahead, so that no copy waits for a table entry ----
+        if (lane == 0) {
+            ta_expect(ta_saddr(&bars[0]), TA_QTILE);
+            ta_tma(ta_saddr(q_s), &map_q, ta_saddr(&bars[0]), h * TA_D, tok0);
+            ta_tma(ta_saddr(q_s + TA_QSLAB), &map_q, ta_saddr(&bars[0]), h * TA_D + 64, tok0);
+        }
+        const int first_col = lo / bs;                        // blocks behind a window may have been given back
+        const int last_col = (hi - 1) / bs;                   // last block column that holds a key of this CTA
+        const int box = min(bs, TA_BN);                       // keys of one copy
+        const int per_tile = TA_BN / box;                     // 1, 2, 4 or 8 copies: chunks of 32 end with a tile
+        const int n_boxes = n_tiles * per_tile;
+        // block of the g-th copy of this CTA; one outside [first key, last key] is replaced by a valid one:
+        // its data is masked, and the softmax warps zero its rows of V
+        auto fetch = [&](int g) -> int {
+            if (g >= n_boxes) return 0;
+            const int col = max(first_col, min((t_begin + g * box) / bs, last_col));
+            int blk = p.block_table[(size_t)slot * p.max_blocks + col];
+            if (blk < 0 || blk >= p.num_blocks) { set_status(p.status, STATUS_BAD_BLOCK); blk = 0; }
+            return blk;
+        };
+        int blk_cur = 0, blk_next = fetch(lane);
+        int issued = 0;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % TA_STAGES;
+            bool ok = true;
+            if (it >= TA_STAGES) ok = ta_wait(ta_saddr(&kv_empty[s]), ((it / TA_STAGES) - 1) & 1, abort_flag, p.status);
+            if (!__all_sync(0xffffffffu, ok && *abort_flag == 0)) break;
+            const uint32_t full = ta_saddr(&kv_full[s]);
+            if (lane == 0) ta_expect(full, 2 * TA_KTILE);
+            unsigned char* ks = kv_s + s * 2 * TA_KTILE;
+            unsigned char* vs = ks + TA_KTILE;
+            const int t0 = t_begin + it * TA_BN;
+            for (int j = 0; j < per_tile; ++j) {
+                const int g = it * per_tile + j;
+                if ((g & 31) == 0) { blk_cur = blk_next; blk_next = fetch(g + 32 + lane); }
+                const int blk = __shfl_sync(0xffffffffu, blk_cur, g & 31);
+                if (lane == 0) {
+                    // row of the pool seen as [rows, d]: the (block, head) slab, and the tile's place in a larger block
+                    const int r0 = j * box;
+                    const int row = (blk * p.n_kv + kvh) * bs + (t0 + r0) % bs;
+                    ta_tma(ta_saddr(ks + r0 * 128), &map_k, full, 0, row);
+                    ta_tma(ta_saddr(ks + TA_KSLAB + r0 * 128), &map_k, full, 64, row);
+                    ta_tma(ta_saddr(vs + r0 * 128), &map_v, full, 0, row);
+                    ta_tma(ta_saddr(vs + TA_KSLAB + r0 * 128), &map_v, full, 64, row);
+                }
+            }
+            issued = it + 1;
+        }
+        // giving up: the copies in flight must land before the CTA's shared memory is released
+        if (lane == 0 && *abort_flag)
+            for (int it = max(0, issued - TA_STAGES); it < issued; ++it)
+                ta_wait(ta_saddr(&kv_full[it % TA_STAGES]), (it / TA_STAGES) & 1, abort_flag + 1, nullptr);
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        // D float, A and B bf16, M 128.  QK^T: N = 64 keys, both K-major; PV: N = 128 dims, B (= V) MN-major
+        const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TA_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint32_t qa = ta_saddr(q_s), pa = ta_saddr(p_s);
+        // S(it) = Q K(it)^T into the S tile it & 1; the barrier s_full[it & 1] completes with it
+        auto issue_qk = [&](int it) -> bool {
+            const int s = it % TA_STAGES;
+            if (!ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t ks = ta_saddr(kv_s + s * 2 * TA_KTILE);
+#pragma unroll
+            for (int kk = 0; kk < TA_D / 16; ++kk) {           // 8 steps over the head dimension
+                const uint32_t inner = (kk & 3) * 32;
+                ta_mma(tmem_s + (it & 1) * TA_BN, ta_desc_k(qa + (kk >> 2) * TA_QSLAB + inner),
+                       ta_desc_k(ks + (kk >> 2) * TA_KSLAB + inner), idesc_qk, kk != 0);
+            }
+            ta_commit(ta_saddr(&s_full[it & 1]));
+            return true;
+        };
+        bool ok = ta_wait(ta_saddr(&bars[0]), 0, abort_flag, p.status);
+        if (ok) ok = issue_qk(0);
+        for (int it = 0; ok && it < n_tiles; ++it) {
+            // the next tile's scores are under way while the softmax warps work on this one: its S tile
+            // was read to the end before p_ready(it - 1), which the last iteration waited for
+            if (it + 1 < n_tiles) { ok = issue_qk(it + 1); if (!ok) break; }
+            ok = ta_wait(ta_saddr(p_ready), it & 1, abort_flag, p.status);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int s = it % TA_STAGES;
+            const uint32_t vs = ta_saddr(kv_s + s * 2 * TA_KTILE + TA_KTILE);
+#pragma unroll
+            for (int kk = 0; kk < TA_BN / 16; ++kk)            // 4 steps over the keys
+                ta_mma(tmem_o, ta_desc_k(pa + kk * 32), ta_desc_mn(vs + kk * 2048, TA_KSLAB), idesc_pv, (it | kk) != 0);
+            ta_commit(ta_saddr(&kv_empty[s]));
+            ta_commit(ta_saddr(o_done));
+        }
+        if (!ok) { ta_commit(ta_saddr(&s_full[0])); ta_commit(ta_saddr(&s_full[1])); ta_commit(ta_saddr(o_done)); }
+    } else if (warp >= 2) {
+        // ---- softmax and epilogue: thread = query row ----
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        const int pos = p_first + r;
+        const float scale_log2 = p.scale * 1.4426950408889634f;   // > 0: the maximum is taken over raw scores
+        float m_run = -INFINITY, l_run = 0.f;                      // running maximum (raw score) and sum
+        bool ok = true;
+        for (int it = 0; it < n_tiles; ++it) {
+            const int t0 = t_begin + it * TA_BN;
+            ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&s_full[it & 1]), (it >> 1) & 1, abort_flag, p.status));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float x[TA_BN];
+            {
+                uint32_t* v = reinterpret_cast<uint32_t*>(x);
+                ta_ld32(tmem_s + (it & 1) * TA_BN + lane_base, v);
+                ta_ld32(tmem_s + (it & 1) * TA_BN + lane_base + 32, v + 32);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            }
+            const bool need_mask = t0 + TA_BN - 1 > p_first || t0 < lo || t0 + TA_BN > hi ||
+                                   (p.window > 0 && t0 < p_first + TA_BM - p.window);
+            if (need_mask) {
+#pragma unroll
+                for (int j = 0; j < TA_BN; ++j) {
+                    const int t = t0 + j;
+                    if (!(t >= lo && t < hi && t <= pos && (p.window <= 0 || pos - t < p.window))) x[j] = -INFINITY;
+                }
+            }
+            float mx = x[0];
+#pragma unroll
+            for (int j = 1; j < TA_BN; ++j) mx = fmaxf(mx, x[j]);
+            // The maximum moves only when it grows by more than 2^8 (P stays below 256, exact enough in
+            // bfloat16 and far from overflow in the 32-bit sums): most tiles then need no rescaling of O
+            float m_new = fmaxf(m_run, mx);
+            if (m_run != -INFINITY && (m_new - m_run) * scale_log2 <= 8.f) m_new = m_run;
+            const float alpha = m_new == m_run ? 1.f : ta_ex2((m_run - m_new) * scale_log2);   // m_run = -inf: 0
+            m_run = m_new;
+            const float m_off = m_new == -INFINITY ? 0.f : m_new * scale_log2;
+            float rs = 0.f;
+            uint32_t packed[TA_BN / 2];
+#pragma unroll
+            for (int j = 0; j < TA_BN; j += 2) {
+                const float p0 = ta_ex2(fmaf(x[j], scale_log2, -m_off));
+                const float p1 = ta_ex2(fmaf(x[j + 1], scale_log2, -m_off));
+                rs += p0 + p1;
+                const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+            }
+            l_run = l_run * alpha + rs;
+            // The previous P V must be complete before P is overwritten and before O is touched;
+            // then O *= alpha where a maximum moved
+            if (it > 0) {
+                ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(o_done), (it - 1) & 1, abort_flag, p.status));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < TA_D; c0 += 32) {
+                        uint32_t v[32];
+                        ta_ld32(tmem_o + lane_base + c0, v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+                        ta_st32(tmem_o + lane_base + c0, v);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            // P as bfloat16 into shared memory: K-major rows of 128 bytes, 16-byte chunks swizzled by the row
+            unsigned char* prow = p_s + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
+                    make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+            // Rows of V that belong to no key of this request (the unused tail of its last cache block, a
+            // block that stands in for one outside its range) may hold anything, even NaN, and 0 * NaN is
+            // NaN: zero them.  The tile has landed (S was computed from it).
+            if (r < TA_BN && (t0 + r < lo || t0 + r >= hi)) {
+                unsigned char* vrow = kv_s + (it % TA_STAGES) * 2 * TA_KTILE + TA_KTILE + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    *reinterpret_cast<uint4*>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vrow + TA_KSLAB + c * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            // P and V (generic-proxy stores) must be visible to the tensor core's reads of shared memory
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            ta_arrive(ta_saddr(p_ready));
+        }
+        if (ok) ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(o_done), (n_tiles - 1) & 1, abort_flag, p.status));
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + ((size_t)(tok0 + r) * p.n_q + h) * TA_D;
+#pragma unroll 1
+            for (int c0 = 0; c0 < TA_D; c0 += 32) {
+                uint32_t v[32];
+                ta_ld32(tmem_o + lane_base + c0, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < nq) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]) * inv,
+                                                                            __uint_as_float(v[j + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&pk);
+                        }
+                        *reinterpret_cast<uint4*>(orow + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------
+typedef CUresult (*TaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static TaEncodeFn ta_encode_fn() {
+    static TaEncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<TaEncodeFn>(sym);
+    }
+    return fn;
+}
+
+// bf16 matrix [rows, cols] read in boxes of box_rows x 64 columns with the 128-byte swizzle
+static int ta_map(const void* ptr, long long rows, int cols, int box_rows, CUtensorMap* out) {
+    static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    auto key = std::make_tuple(ptr, rows, cols, box_rows);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    TaEncodeFn fn = ta_encode_fn();
+    if (fn == nullptr) return 1;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return 0;
+}
+
+// Returns 1 when it does not take the sizes (the caller falls back to the mma.sync kernel):
+// head size 128, block size a multiple of 8 that divides 128, no split of the keys.
+int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_q_len, cudaStream_t stream) {
+    if (p.d != TA_D || p.n_splits != 1) return 1;
+    const int bs = p.block_size;
+    if (bs < 8 || bs > 128 || bs % 8 != 0 || 128 % bs != 0) return 1;
+    if (p.n_q > 65535 || n_rows > 65535) return 1;
+    CUtensorMap mq, mk, mv;
+    if (ta_map(p.q, T, p.n_q * TA_D, TA_BM, &mq) != 0) return 1;
+    const long long pool_rows = (long long)p.num_blocks * p.n_kv * bs;
+    const int box = bs < TA_BN ? bs : TA_BN;
+    if (ta_map(p.k_pool, pool_rows, TA_D, box, &mk) != 0) return 1;
+    if (ta_map(p.v_pool, pool_rows, TA_D, box, &mv) != 0) return 1;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TA_SMEM);
+        if (e != cudaSuccess) return fail(-3, "attention: cannot get %d bytes of shared memory: %s", TA_SMEM, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int q_tiles = (max_q_len + TA_BM - 1) / TA_BM;
+    dim3 grid(q_tiles, p.n_q, n_rows);
+    attn_prefill_tcgen05_kernel<<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p);
+    return check_launch("attention_prefill_tcgen05");
+}
+
+}  // namespace fd

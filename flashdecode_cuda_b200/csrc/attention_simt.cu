@@ -386,7 +386,10 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
         if (rc == 0 && p.counters != nullptr) return 0;
         p.counters = nullptr;
     }
-    else if (use_mma && dtype == 1) rc = launch_attn_prefill_mma(p, n_rows, max_q_len, stream);
+    else if (use_mma && dtype == 1) {
+        rc = use_mma == 2 ? 1 : launch_attn_prefill_tcgen05(p, n_rows, T, max_q_len, stream);
+        if (rc == 1) rc = launch_attn_prefill_mma(p, n_rows, max_q_len, stream);
+    }
     if (rc == 1)
         rc = dtype == 0 ? launch_attn<float>(p, n_rows, max_q_len, stream)
                         : launch_attn<bf16>(p, n_rows, max_q_len, stream);
@@ -428,4 +431,18 @@ extern "C" int fd_attention(const void* q, const void* k_pool, const void* v_poo
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
                           window, n_splits, split_len, scratch, counters, status, 1, stream);
+}
+
+// The same without the tcgen05 kernel: prompts go to the mma.sync kernel (head sizes other than 128 always
+// do; this entry lets tests and measurements reach it at 128 too).
+extern "C" int fd_attention_mma_sync(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
+                                     const int* block_table, int max_blocks, int num_blocks, int block_size,
+                                     const int* tok_row, const int* row_slot, const int* row_q_start,
+                                     const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
+                                     int max_q_len, int n_q, int n_kv, int d, float scale, int window,
+                                     int n_splits, int split_len, float* scratch, int* counters, int* status,
+                                     cudaStream_t stream) {
+    return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
+                          row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
+                          window, n_splits, split_len, scratch, counters, status, 2, stream);
 }

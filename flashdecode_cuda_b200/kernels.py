@@ -88,6 +88,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attn_simt_qt": [I],
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
+        "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
     }
     for name, args in sigs.items():
@@ -334,7 +335,7 @@ def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, 
             num_blocks, block_size, _ptr(tok_row), _ptr(row_slot), _ptr(row_q_start), _ptr(row_q_len),
             _ptr(row_ctx_len), n_rows, T, max_q_len, n_q, n_kv, head_dim, float(scale), int(window), n_splits,
             split_len, _ptr(scratch)]
-    if fn_name == "fd_attention":
+    if fn_name != "fd_attention_simt":
         fused = n_splits > 1 and max_q_len == 1 and q.dtype == torch.bfloat16
         args.append(_ptr(_counters(q.device, n_rows * n_kv)) if fused else None)
     args += [_ptr(status), _stream()]
@@ -353,6 +354,19 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
     _attention("fd_attention", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
                row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
                scratch, status)
+
+
+def attention_mma_sync(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                       block_table: torch.Tensor, tok_row: torch.Tensor, row_slot: torch.Tensor,
+                       row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
+                       n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
+                       window: int = 0, n_splits: int = 1, split_len: int = 0,
+                       scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+    """The same with prompts on the mma.sync kernel even at head size 128, where
+    ``attention`` takes the tcgen05 kernel."""
+    _attention("fd_attention_mma_sync", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start,
+               row_q_len, row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits,
+               split_len, scratch, status)
 
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,

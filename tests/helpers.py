@@ -41,6 +41,12 @@ TINY = {
     "D": _qwen2(num_hidden_layers=2, hidden_size=128, num_attention_heads=6, num_key_value_heads=2,
                 head_dim=64, intermediate_size=192, vocab_size=320, rope_theta=250000.0, rms_norm_eps=2e-6,
                 tie_word_embeddings=True, max_position_embeddings=1024),
+    # head_dim 128 (the tcgen05 attention and, from 128 prompt tokens on, the tcgen05 products), one KV
+    # head shared by 3 query heads, a window of 40 keys on the second layer
+    "E": _qwen2(num_hidden_layers=2, hidden_size=192, num_attention_heads=3, num_key_value_heads=1,
+                head_dim=128, intermediate_size=320, vocab_size=288, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, max_position_embeddings=1024, use_sliding_window=True,
+                sliding_window=40, max_window_layers=1),
 }
 NO_BIAS = {"C"}
 

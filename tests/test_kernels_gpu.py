@@ -459,7 +459,7 @@ def attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window
 
 
 def run_attention(dtype, n_q, n_kv, d, bs, ctx, new, window=0, n_splits=1, split_len=0, seed=7,
-                  spike=None, pad_rows=0, fn=None):
+                  spike=None, pad_rows=0, fn=None, qk_scale=1.0, ramp=0.0):
     g = torch.Generator().manual_seed(seed)
     dt = DT[dtype]
     lens = [c + n for c, n in zip(ctx, new)]
@@ -467,7 +467,13 @@ def run_attention(dtype, n_q, n_kv, d, bs, ctx, new, window=0, n_splits=1, split
     k_seqs = [torch.randn(n, n_kv, d, generator=g).to(dt) for n in lens]
     v_seqs = [torch.randn(n, n_kv, d, generator=g).to(dt) for n in lens]
     T = sum(new)
-    q = torch.randn(T, n_q * d, generator=g).to(dt)
+    q = (torch.randn(T, n_q * d, generator=g) * qk_scale).to(dt)
+    if ramp:
+        # scores that rise along the keys by `ramp` (in units of the softmax's exponent) per key
+        u = torch.zeros(d)
+        u[0] = 1.0
+        k_seqs = [(k.float() * (1 - u) + u * ramp * math.sqrt(d) * torch.arange(len(k)).view(-1, 1, 1)).to(dt) for k in k_seqs]
+        q = (q.float().view(T, n_q, d) * (1 - u) + u).view(T, n_q * d).to(dt)
     if spike is not None:
         # one far key and one query made to match: its score stands out, so a
         # kernel that drops that key (a split boundary, a window edge) shows
@@ -562,27 +568,53 @@ def test_attention_decode_tensor_cores(n_q, n_kv, d, bs, n_splits, split_len):
         assert float(pad.float().abs().max()) == 0.0
 
 
+# head size 128: K.attention takes the tcgen05 kernel, K.attention_mma_sync the mma.sync one
+PROMPT_KERNELS = [K.attention, K.attention_mma_sync]
+
+
+@pytest.mark.parametrize("fn", PROMPT_KERNELS, ids=["auto", "mma_sync"])
 @pytest.mark.parametrize("n_q,n_kv,d,bs", [(12, 2, 128, 16), (7, 1, 128, 4), (5, 5, 64, 32), (6, 2, 64, 16), (28, 4, 128, 8)])
-def test_attention_prompts_tensor_cores(n_q, n_kv, d, bs):
-    """The dispatcher's tensor-core kernel for bfloat16 prompt steps: unequal
+def test_attention_prompts_tensor_cores(n_q, n_kv, d, bs, fn):
+    """The dispatcher's tensor-core kernels for bfloat16 prompt steps: unequal
     lengths around the 64-token tile edges, some continuing a cached prefix."""
     got, want, _ = run_attention("bfloat16", n_q, n_kv, d, bs, ctx=[0, 0, 13, 0, 100, 64], new=[1, 64, 65, 130, 30, 63],
-                                 fn=K.attention)
+                                 fn=fn)
     assert rel(got, want) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("fn", PROMPT_KERNELS, ids=["auto", "mma_sync"])
 @pytest.mark.parametrize("window", [1, 5, 63, 64, 65, 200])
-def test_attention_prompts_tensor_cores_window_and_far_key(window):
-    got, want, _ = run_attention("bfloat16", 6, 2, 64, 16, ctx=[0, 90, 7], new=[150, 70, 1], window=window, fn=K.attention)
+def test_attention_prompts_tensor_cores_window_and_far_key(window, fn):
+    got, want, _ = run_attention("bfloat16", 6, 2, 64, 16, ctx=[0, 90, 7], new=[150, 70, 1], window=window, fn=fn)
     assert rel(got, want) < TOL["bfloat16"]
     if window == 200:
         for key_pos in (0, 63, 64, 400, 639, 698):
             got, want, _ = run_attention("bfloat16", 12, 2, 128, 16, ctx=[0, 0], new=[700, 3], spike=(0, key_pos),
-                                         fn=K.attention)
+                                         fn=fn)
             assert rel(got, want) < TOL["bfloat16"], key_pos
             got, want, _ = run_attention("bfloat16", 12, 2, 128, 16, ctx=[640, 0], new=[60, 3], spike=(0, key_pos),
-                                         fn=K.attention)
+                                         fn=fn)
             assert rel(got, want) < TOL["bfloat16"], key_pos
+
+
+def test_attention_prompts_tcgen05_large_scores():
+    """The tcgen05 kernel moves a row's running maximum only when it grows by more than 2^8:
+    scores that rise steadily along the keys (each tile a little above the last), scores that
+    jump far, and a long prompt over several hundred keys must all come out the same."""
+    for qk_scale, ramp in ((1.0, 0.0), (6.0, 0.0), (30.0, 0.0), (1.0, 0.05), (1.0, 0.125), (1.0, 1.0), (0.0, 0.03)):
+        got, want, _ = run_attention("bfloat16", 4, 2, 128, 16, ctx=[0, 300], new=[520, 200], fn=K.attention,
+                                     qk_scale=qk_scale, ramp=ramp)
+        assert rel(got, want) < TOL["bfloat16"], (qk_scale, ramp)
+
+
+@pytest.mark.parametrize("window", [1, 40, 127, 128, 129, 300])
+@pytest.mark.parametrize("bs", [8, 16, 64, 128])
+def test_attention_prompts_tcgen05_window(window, bs):
+    """Head size 128 goes to the tcgen05 kernel: windows around its tiles of 64 keys and 128
+    queries, every block size it takes, prompts that continue a cached prefix."""
+    got, want, _ = run_attention("bfloat16", 6, 2, 128, bs, ctx=[0, 150, 7, 256], new=[260, 130, 1, 128], window=window,
+                                 fn=K.attention)
+    assert rel(got, want) < TOL["bfloat16"]
 
 
 @pytest.mark.parametrize("window", [1, 16, 17, 100])

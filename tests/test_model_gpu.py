@@ -11,7 +11,7 @@ from helpers import TINY, TOL, oracle_logits, prompts_for, rel_err, write_folder
 
 pytestmark = pytest.mark.gpu
 
-CONFIGS = ["A", "B", "C", "D"]
+CONFIGS = ["A", "B", "C", "D", "E"]
 DTYPES = ["float32", "bfloat16"]
 
 
@@ -27,7 +27,8 @@ def engines(folders):
 
 
 def _lengths(name):
-    return {"A": [5, 11, 17, 64], "B": [1, 7, 16, 33, 100], "C": [3, 24, 25, 49, 130], "D": [2, 63, 64, 65, 200]}[name]
+    return {"A": [5, 11, 17, 64], "B": [1, 7, 16, 33, 100], "C": [3, 24, 25, 49, 130], "D": [2, 63, 64, 65, 200],
+            "E": [3, 128, 129, 300]}[name]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -35,7 +36,7 @@ def _lengths(name):
 @pytest.mark.parametrize("block_size", [4, 16])
 def test_each_request_alone_and_whole(engines, folders, name, dtype, block_size):
     eng = engines[(name, dtype)]
-    cache = eng.model.new_cache(max_tokens=256, block_size=block_size)
+    cache = eng.model.new_cache(max_tokens=-(-max(_lengths(name)) // 64) * 64, block_size=block_size)
     for p in prompts_for(TINY[name]["vocab_size"], _lengths(name), seed=1):
         slot = cache.admit()
         got = eng.model.step(cache, [slot], [p], "all")
@@ -97,7 +98,7 @@ def test_unequal_batches_one_after_another(engines, folders, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["B", "C", "D"])
+@pytest.mark.parametrize("name", ["B", "C", "D", "E"])
 def test_long_decoding(engines, folders, name, dtype):
     """Two tokens of prompt, then 200 decoded one by one in a batch of two."""
     eng = engines[(name, dtype)]
