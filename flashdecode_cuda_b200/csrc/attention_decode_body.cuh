@@ -1,0 +1,331 @@
+// The body of the split-KV decode attention kernel on the tensor cores, as a function of a
+// group of four warps, so that it serves both the kernel of its own (attention_decode_mma.cu,
+// where the group is the CTA) and the persistent kernel that runs a whole stack of layers
+// (decode_stack.cu, where a CTA holds several groups).
+#pragma once
+
+#include <math.h>
+
+#include "attention.cuh"
+#include "mma_utils.cuh"
+
+namespace fd {
+
+constexpr int DM_WARPS = 4;
+constexpr int DM_THREADS = DM_WARPS * 32;
+constexpr int DM_TILE = 16;       // keys per warp tile
+constexpr int DM_STAGES = 3;     // tiles of a warp under way or in use: two loads always in flight
+
+
+// barriers of a group: the whole CTA, or 128 threads of it that share the named barrier `id` (1..15)
+struct CtaSync {
+    __device__ __forceinline__ void operator()() const { __syncthreads(); }
+};
+struct GroupSync {
+    int id;
+    __device__ __forceinline__ void operator()() const { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+};
+
+// shared memory of one group: queries, the warps' staging areas, their softmax state, one flag
+template <int D>
+__host__ __device__ constexpr size_t dm_smem_bytes() {
+    return 16 * D * 2 + (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * D * 2 + 2 * DM_WARPS * 16 * sizeof(float) + 16;
+}
+
+// One (sequence, KV head, split) by a group of DM_WARPS warps.  `tid`: the thread's index in
+// the group; `smem`: the group's dm_smem_bytes<D>() of shared memory; `sync`: a barrier of the
+// group's threads.  QREG: keep the query fragments in registers (32 at D = 128) instead of
+// reading them from shared memory for every tile.  Every thread of the group returns together.
+template <int D, bool QREG, typename Sync>
+__device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int split, const int kvh, const int b,
+                                                 unsigned char* smem, const int tid, Sync sync) {
+    constexpr int CPR = D / 8;                 // 16-byte chunks per row
+    constexpr int TILE_BYTES = DM_TILE * D * 2;
+    constexpr int WARP_BYTES = DM_STAGES * 2 * TILE_BYTES;   // K and V, every stage
+    const int slot = p.row_slot[b];
+    const int tok = p.row_q_start[b];
+    const int G = p.G;
+    if (slot < 0) {
+        // padding row: zeros, written here when no merge kernel follows
+        if (p.counters != nullptr && split == 0)
+            for (int e = tid; e < G * D; e += DM_THREADS)
+                static_cast<__nv_bfloat16*>(p.out)[((size_t)tok * p.n_q + kvh * G) * D + e] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int ctx = p.row_ctx_len[b];
+    int lo = p.window > 0 ? max(0, ctx - p.window + 1) : 0;
+    int hi = ctx + 1;                           // the new token's own key is already in the cache
+    if (p.n_splits > 1) {
+        lo = max(lo, split * p.split_len);
+        hi = min(hi, (split + 1) * p.split_len);
+    }
+
+    unsigned char* q_s = smem;                                  // [16][D] bf16, swizzled
+    unsigned char* kv_s = smem + 16 * D * 2;                    // per warp: [stage][K|V][16][D]
+    float* m_s = reinterpret_cast<float*>(kv_s + DM_WARPS * WARP_BYTES);   // [warps][16]
+    float* l_s = m_s + DM_WARPS * 16;
+    int* is_last = reinterpret_cast<int*>(l_s + DM_WARPS * 16);
+
+    const int lane = tid & 31, warp = tid >> 5;
+    const __nv_bfloat16* qg = static_cast<const __nv_bfloat16*>(p.q);
+    const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(p.k_pool);
+    const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(p.v_pool);
+
+    // queries: rows 0..G-1 are the heads of this KV head, the rest zero
+    for (int c = tid; c < 16 * CPR; c += DM_THREADS) {
+        const int r = c / CPR, cc = c - r * CPR;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < G) v = __ldcg(reinterpret_cast<const uint4*>(qg + ((size_t)tok * p.n_q + kvh * G + r) * D + cc * 8));   // L2: written by another CTA just before
+        *reinterpret_cast<uint4*>(q_s + swz<D>(r, cc)) = v;
+    }
+    sync();
+    uint32_t qf[QREG ? D / 16 : 1][4];
+    const int q_mi = lane >> 3, q_r = (q_mi & 1) * 8 + (lane & 7);
+    if (QREG) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+            ldmatrix_x4(smem_u32(q_s + swz<D>(q_r, ks * 2 + (q_mi >> 1))), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY};   // rows lane/4 and lane/4 + 8
+    float l_run[2] = {0.f, 0.f};               // per-thread partial sums (its 4 columns of each tile)
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+
+    unsigned char* my = kv_s + warp * WARP_BYTES;
+    const int bs = p.block_size;
+    const int bs_shift = (bs & (bs - 1)) == 0 ? __ffs(bs) - 1 : -1;     // powers of two: shift and mask
+    const bool tile_in_block = bs_shift >= 4;                           // a 16-key tile then lies in one block
+    const int first_tile = lo / DM_TILE;
+    const int n_tiles = hi > lo ? (hi - 1) / DM_TILE - first_tile + 1 : 0;
+
+    // stage one 16-key tile (keys and values) of this warp
+    auto issue = [&](int j, int stage) {
+        const int t0 = (first_tile + j) * DM_TILE;
+        unsigned char* ks = my + stage * 2 * TILE_BYTES;
+        unsigned char* vs = ks + TILE_BYTES;
+        int tile_blk = -1, tile_off = 0;
+        if (tile_in_block) {
+            tile_blk = p.block_table[(size_t)slot * p.max_blocks + (t0 >> bs_shift)];
+            tile_off = t0 & (bs - 1);
+        }
+#pragma unroll
+        for (int i = 0; i < DM_TILE * CPR / 32; ++i) {
+            const int c = i * 32 + lane;
+            const int r = c / CPR, cc = c - r * CPR;
+            const int t = t0 + r;
+            const __nv_bfloat16* ksrc = kp;
+            const __nv_bfloat16* vsrc = vp;
+            int bytes = 0;
+            if (t >= lo && t < hi) {
+                int blk, in_blk;
+                if (tile_in_block) { blk = tile_blk; in_blk = tile_off + r; }
+                else if (bs_shift >= 0) { blk = p.block_table[(size_t)slot * p.max_blocks + (t >> bs_shift)]; in_blk = t & (bs - 1); }
+                else { const int col = t / bs; blk = p.block_table[(size_t)slot * p.max_blocks + col]; in_blk = t - col * bs; }
+                if (blk < 0 || blk >= p.num_blocks) {
+                    set_status(p.status, STATUS_BAD_BLOCK);
+                } else {
+                    const size_t off = (((size_t)blk * p.n_kv + kvh) * bs + in_blk) * D + cc * 8;
+                    ksrc = kp + off;
+                    vsrc = vp + off;
+                    bytes = 16;
+                }
+            }
+            cp_async16(smem_u32(ks + swz<D>(r, cc)), ksrc, bytes);     // 0 bytes: the chunk is zero-filled
+            cp_async16(smem_u32(vs + swz<D>(r, cc)), vsrc, bytes);
+        }
+        cp_async_commit();
+    };
+
+    int n_mine = 0;
+    for (int j = warp; j < n_tiles; j += DM_WARPS) ++n_mine;
+    // prologue: the first DM_STAGES - 1 tiles (an empty group keeps the count uniform)
+#pragma unroll
+    for (int st = 0; st < DM_STAGES - 1; ++st) {
+        if (st < n_mine) issue(warp + st * DM_WARPS, st);
+        else cp_async_commit();
+    }
+    for (int i = 0; i < n_mine; ++i) {
+        const int j = warp + i * DM_WARPS;
+        cp_async_wait<DM_STAGES - 2>();       // tile i has landed
+        __syncwarp();
+        // refill the stage that iteration i - 1 finished with
+        if (i + DM_STAGES - 1 < n_mine) issue(j + (DM_STAGES - 1) * DM_WARPS, (i + DM_STAGES - 1) % DM_STAGES);
+        else cp_async_commit();
+        const unsigned char* ks = my + (i % DM_STAGES) * 2 * TILE_BYTES;
+        const unsigned char* vs = ks + TILE_BYTES;
+
+        // S = Q K^T for 16 keys: two n-tiles of 8 keys
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const int mi = lane >> 3;
+            const int r = (mi >> 1) * 8 + (lane & 7);            // key row of this lane's matrix
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(smem_u32(ks + swz<D>(r, kk * 2 + (mi & 1))), b0, b1, b2, b3);
+                uint32_t a0, a1, a2, a3;
+                if (QREG) { a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3]; }
+                else ldmatrix_x4(smem_u32(q_s + swz<D>(q_r, kk * 2 + (q_mi >> 1))), a0, a1, a2, a3);
+                mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
+                mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        // mask and online softmax (base 2); this thread's keys: t0 + (lane%4)*2 + {0,1} (+8)
+        const int t0 = (first_tile + j) * DM_TILE;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int t = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                const float v = (t >= lo && t < hi) ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            alpha[h] = m_new == -INFINITY ? 1.f : exp2f(m_run[h] - m_new);
+            m_run[h] = m_new;
+        }
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = m_run[e >> 1] == -INFINITY ? 0.f : exp2f(s[nt][e] - m_run[e >> 1]);
+                s[nt][e] = pv;
+                rs[e >> 1] += pv;
+            }
+        l_run[0] = l_run[0] * alpha[0] + rs[0];
+        l_run[1] = l_run[1] * alpha[1] + rs[1];
+        const uint32_t pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
+        const uint32_t pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
+        // O = O * alpha + P V
+        const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
+        {
+            const int mi = lane >> 3;
+            const int r = (mi & 1) * 8 + (lane & 7);             // key row
+#pragma unroll
+            for (int np = 0; np < D / 16; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(smem_u32(vs + swz<D>(r, np * 2 + (mi >> 1))), b0, b1, b2, b3);
+                float* oa = o[np * 2];
+                float* ob = o[np * 2 + 1];
+                if (rescale) {       // most tiles leave every running maximum as it was
+                    oa[0] *= alpha[0]; oa[1] *= alpha[0]; oa[2] *= alpha[1]; oa[3] *= alpha[1];
+                    ob[0] *= alpha[0]; ob[1] *= alpha[0]; ob[2] *= alpha[1]; ob[3] *= alpha[1];
+                }
+                mma_bf16(oa, pa0, pa1, pa2, pa3, b0, b1);
+                mma_bf16(ob, pa0, pa1, pa2, pa3, b2, b3);
+            }
+        }
+        __syncwarp();      // every lane is done with this stage before it is refilled
+    }
+
+    cp_async_wait<0>();
+    // per-warp results to shared memory: O as float [16][D] in the warp's own staging area
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    float* o_w = reinterpret_cast<float*>(my);
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+            *reinterpret_cast<float2*>(o_w + r0 * D + nt * 8 + c0) = make_float2(o[nt][0], o[nt][1]);
+            *reinterpret_cast<float2*>(o_w + (r0 + 8) * D + nt * 8 + c0) = make_float2(o[nt][2], o[nt][3]);
+        }
+        if ((lane & 3) == 0) {
+            m_s[warp * 16 + r0] = m_run[0];  m_s[warp * 16 + r0 + 8] = m_run[1];
+            l_s[warp * 16 + r0] = l_run[0];  l_s[warp * 16 + r0 + 8] = l_run[1];
+        }
+    }
+    sync();
+
+    // merge the warps; one (head, dim) pair per thread step
+    constexpr float LN2 = 0.6931471805599453f;
+    for (int e = tid; e < G * D; e += DM_THREADS) {
+        const int r = e / D, j = e - r * D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DM_WARPS; ++w) m = fmaxf(m, m_s[w * 16 + r]);
+        float l = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < DM_WARPS; ++w) {
+            const float mw = m_s[w * 16 + r];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+            l += l_s[w * 16 + r] * f;
+            a += reinterpret_cast<const float*>(kv_s + w * WARP_BYTES)[r * D + j] * f;
+        }
+        const size_t row = (size_t)tok * p.n_q + kvh * G + r;
+        if (p.n_splits > 1) {
+            const size_t pi = row * p.n_splits + split;
+            p.part_acc[pi * D + j] = a;
+            if (j == 0) { p.part_m[pi] = m * LN2; p.part_l[pi] = l; }   // natural-log units for the merge
+        } else {
+            static_cast<__nv_bfloat16*>(p.out)[row * D + j] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
+        }
+    }
+    if (p.n_splits == 1 || p.counters == nullptr) return;
+
+    // The CTA that finishes last for this (sequence, KV head) merges the splits: no CTA waits for
+    // another.  Its partial results are made visible device-wide before it announces itself.
+    __threadfence();
+    sync();
+    if (tid == 0) {
+        int* cnt = p.counters + (size_t)b * p.n_kv + kvh;
+        const int old = atomicAdd(cnt, 1);
+        *is_last = old == p.n_splits - 1;
+        if (*is_last) *cnt = 0;                      // ready for the next launch
+    }
+    sync();
+    if (!*is_last) return;
+    __threadfence();
+    // weights e^(m_s - m) / l of every (head, split), one warp per head; the staging area is free now
+    float* wgt = reinterpret_cast<float*>(kv_s);     // [G][n_splits]
+    const int ns = p.n_splits;
+    for (int r = warp; r < G; r += DM_WARPS) {
+        const size_t base = ((size_t)tok * p.n_q + kvh * G + r) * ns;
+        float m = -INFINITY;
+        for (int s = lane; s < ns; s += 32)
+            if (__ldcg(p.part_l + base + s) > 0.f) m = fmaxf(m, __ldcg(p.part_m + base + s));
+        m = warp_max(m);
+        float lsum = 0.f;
+        for (int s = lane; s < ns; s += 32) {
+            const float ls = __ldcg(p.part_l + base + s);
+            const float w = ls > 0.f ? expf(__ldcg(p.part_m + base + s) - m) : 0.f;
+            wgt[r * ns + s] = w;
+            lsum += ls * w;
+        }
+        lsum = warp_sum(lsum);
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        for (int s = lane; s < ns; s += 32) wgt[r * ns + s] *= inv;
+    }
+    sync();
+    for (int e = tid; e < G * D; e += DM_THREADS) {
+        const int r = e / D, j = e - r * D;
+        const size_t row = (size_t)tok * p.n_q + kvh * G + r;
+        const float* pa = p.part_acc + row * ns * D + j;
+        const float* w = wgt + r * ns;
+        float a = 0.f;
+        int s = 0;
+        for (; s + 4 <= ns; s += 4) {
+            const float a0 = __ldcg(pa + (size_t)(s + 0) * D), a1 = __ldcg(pa + (size_t)(s + 1) * D);
+            const float a2 = __ldcg(pa + (size_t)(s + 2) * D), a3 = __ldcg(pa + (size_t)(s + 3) * D);
+            a = fmaf(a0, w[s], a); a = fmaf(a1, w[s + 1], a); a = fmaf(a2, w[s + 2], a); a = fmaf(a3, w[s + 3], a);
+        }
+        for (; s < ns; ++s) a = fmaf(__ldcg(pa + (size_t)s * D), w[s], a);
+        static_cast<__nv_bfloat16*>(p.out)[row * D + j] = __float2bfloat16_rn(a);
+    }
+}
+
+}  // namespace fd
