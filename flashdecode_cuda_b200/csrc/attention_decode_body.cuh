@@ -71,20 +71,18 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
     const __nv_bfloat16* kp = static_cast<const __nv_bfloat16*>(p.k_pool);
     const __nv_bfloat16* vp = static_cast<const __nv_bfloat16*>(p.v_pool);
 
-    // queries: rows 0..G-1 are the heads of this KV head, the rest zero
-    for (int c = tid; c < 16 * CPR; c += DM_THREADS) {
-        const int r = c / CPR, cc = c - r * CPR;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < G) v = __ldcg(reinterpret_cast<const uint4*>(qg + ((size_t)tok * p.n_q + kvh * G + r) * D + cc * 8));   // L2: written by another CTA just before
-        *reinterpret_cast<uint4*>(q_s + swz<D>(r, cc)) = v;
-    }
-    sync();
-    uint32_t qf[QREG ? D / 16 : 1][4];
-    const int q_mi = lane >> 3, q_r = (q_mi & 1) * 8 + (lane & 7);
-    if (QREG) {
+    // queries: rows 0..G-1 are the heads of this KV head, the rest zero.  Their loads are issued here
+    // and land in shared memory after the first key tiles have been asked for.
+    constexpr int Q_PER_THREAD = (16 * CPR + DM_THREADS - 1) / DM_THREADS;
+    uint4 q_regs[Q_PER_THREAD];
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-            ldmatrix_x4(smem_u32(q_s + swz<D>(q_r, ks * 2 + (q_mi >> 1))), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    for (int i = 0; i < Q_PER_THREAD; ++i) {
+        const int c = tid + i * DM_THREADS;
+        const int r = c / CPR, cc = c - r * CPR;
+        q_regs[i] = make_uint4(0, 0, 0, 0);
+        // L2 load: in the persistent kernel another CTA wrote the queries just before
+        if (c < 16 * CPR && r < G)
+            q_regs[i] = __ldcg(reinterpret_cast<const uint4*>(qg + ((size_t)tok * p.n_q + kvh * G + r) * D + cc * 8));
     }
 
     float o[D / 8][4];
@@ -101,19 +99,52 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
     const int first_tile = lo / DM_TILE;
     const int n_tiles = hi > lo ? (hi - 1) / DM_TILE - first_tile + 1 : 0;
 
-    // stage one 16-key tile (keys and values) of this warp
-    auto issue = [&](int j, int stage) {
+    int n_mine = 0;
+    for (int j = warp; j < n_tiles; j += DM_WARPS) ++n_mine;
+    // Blocks of this warp's tiles, 32 at a time, one per lane: fetched together and ahead of use, so that
+    // no tile's copies wait for a table entry of their own.
+    int blk_base = 0, blk_reg = -1;
+    auto fetch_blocks = [&](int base) {
+        blk_base = base;
+        blk_reg = -1;
+        const int i = base + lane;
+        if (tile_in_block && i < n_mine)
+            blk_reg = p.block_table[(size_t)slot * p.max_blocks + (((first_tile + warp + i * DM_WARPS) * DM_TILE) >> bs_shift)];
+    };
+    fetch_blocks(0);
+
+    // stage the warp's i-th 16-key tile (keys and values); called with i ascending
+    auto issue = [&](int i, int stage) {
+        const int j = warp + i * DM_WARPS;
         const int t0 = (first_tile + j) * DM_TILE;
         unsigned char* ks = my + stage * 2 * TILE_BYTES;
         unsigned char* vs = ks + TILE_BYTES;
         int tile_blk = -1, tile_off = 0;
         if (tile_in_block) {
-            tile_blk = p.block_table[(size_t)slot * p.max_blocks + (t0 >> bs_shift)];
+            if (i >= blk_base + 32) fetch_blocks(i);
+            tile_blk = __shfl_sync(0xffffffffu, blk_reg, i - blk_base);
             tile_off = t0 & (bs - 1);
-        }
+            if (t0 >= lo && t0 + DM_TILE <= hi && tile_blk >= 0 && tile_blk < p.num_blocks) {
+                // the usual case, a whole tile inside one block: one base address, constant offsets per lane
+                // (the address arithmetic of the general path below cost more than the tile's tensor work)
+                const size_t base = (((size_t)tile_blk * p.n_kv + kvh) * bs + tile_off) * D;
+                const __nv_bfloat16* kb = kp + base;
+                const __nv_bfloat16* vb = vp + base;
 #pragma unroll
-        for (int i = 0; i < DM_TILE * CPR / 32; ++i) {
-            const int c = i * 32 + lane;
+                for (int u = 0; u < DM_TILE * CPR / 32; ++u) {
+                    const int c = u * 32 + lane;
+                    const int r = c / CPR, cc = c - r * CPR;
+                    cp_async16(smem_u32(ks + swz<D>(r, cc)), kb + r * D + cc * 8, 16);
+                    cp_async16(smem_u32(vs + swz<D>(r, cc)), vb + r * D + cc * 8, 16);
+                }
+                cp_async_commit();
+                return;
+            }
+        }
+        // tiles at the edges of the range, small or odd block sizes, bad table entries: chunk by chunk
+#pragma unroll
+        for (int u = 0; u < DM_TILE * CPR / 32; ++u) {
+            const int c = u * 32 + lane;
             const int r = c / CPR, cc = c - r * CPR;
             const int t = t0 + r;
             const __nv_bfloat16* ksrc = kp;
@@ -139,20 +170,33 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
         cp_async_commit();
     };
 
-    int n_mine = 0;
-    for (int j = warp; j < n_tiles; j += DM_WARPS) ++n_mine;
     // prologue: the first DM_STAGES - 1 tiles (an empty group keeps the count uniform)
 #pragma unroll
     for (int st = 0; st < DM_STAGES - 1; ++st) {
-        if (st < n_mine) issue(warp + st * DM_WARPS, st);
+        if (st < n_mine) issue(st, st);
         else cp_async_commit();
+    }
+    // now the queries: to shared memory, and from there as tensor-core fragments
+#pragma unroll
+    for (int i = 0; i < Q_PER_THREAD; ++i) {
+        const int c = tid + i * DM_THREADS;
+        const int r = c / CPR, cc = c - r * CPR;
+        if (c < 16 * CPR) *reinterpret_cast<uint4*>(q_s + swz<D>(r, cc)) = q_regs[i];
+    }
+    sync();
+    uint32_t qf[QREG ? D / 16 : 1][4];
+    const int q_mi = lane >> 3, q_r = (q_mi & 1) * 8 + (lane & 7);
+    if (QREG) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+            ldmatrix_x4(smem_u32(q_s + swz<D>(q_r, ks * 2 + (q_mi >> 1))), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
     }
     for (int i = 0; i < n_mine; ++i) {
         const int j = warp + i * DM_WARPS;
         cp_async_wait<DM_STAGES - 2>();       // tile i has landed
         __syncwarp();
         // refill the stage that iteration i - 1 finished with
-        if (i + DM_STAGES - 1 < n_mine) issue(j + (DM_STAGES - 1) * DM_WARPS, (i + DM_STAGES - 1) % DM_STAGES);
+        if (i + DM_STAGES - 1 < n_mine) issue(i + DM_STAGES - 1, (i + DM_STAGES - 1) % DM_STAGES);
         else cp_async_commit();
         const unsigned char* ks = my + (i % DM_STAGES) * 2 * TILE_BYTES;
         const unsigned char* vs = ks + TILE_BYTES;
@@ -290,19 +334,27 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
     sync();
     if (!*is_last) return;
     __threadfence();
-    // weights e^(m_s - m) / l of every (head, split), one warp per head; the staging area is free now
-    float* wgt = reinterpret_cast<float*>(kv_s);     // [G][n_splits]
+    // The staging area is free now.  First every (head, split)'s maximum and sum, fetched in one round trip;
+    // then the weights e^(m_s - m) / l, one warp per head; then the weighted sum of the splits' outputs.
     const int ns = p.n_splits;
+    float* wgt = reinterpret_cast<float*>(kv_s);     // [G][ns]: the sums, then the weights
+    float* mx_s = wgt + G * ns;                      // [G][ns]: the maxima (-inf for an empty split)
+    for (int e = tid; e < G * ns; e += DM_THREADS) {
+        const int r = e / ns, s = e - r * ns;
+        const size_t idx = ((size_t)tok * p.n_q + kvh * G + r) * ns + s;
+        const float ls = __ldcg(p.part_l + idx), ms = __ldcg(p.part_m + idx);
+        wgt[e] = ls;
+        mx_s[e] = ls > 0.f ? ms : -INFINITY;
+    }
+    sync();
     for (int r = warp; r < G; r += DM_WARPS) {
-        const size_t base = ((size_t)tok * p.n_q + kvh * G + r) * ns;
         float m = -INFINITY;
-        for (int s = lane; s < ns; s += 32)
-            if (__ldcg(p.part_l + base + s) > 0.f) m = fmaxf(m, __ldcg(p.part_m + base + s));
+        for (int s = lane; s < ns; s += 32) m = fmaxf(m, mx_s[r * ns + s]);
         m = warp_max(m);
         float lsum = 0.f;
         for (int s = lane; s < ns; s += 32) {
-            const float ls = __ldcg(p.part_l + base + s);
-            const float w = ls > 0.f ? expf(__ldcg(p.part_m + base + s) - m) : 0.f;
+            const float ls = wgt[r * ns + s];
+            const float w = ls > 0.f ? expf(mx_s[r * ns + s] - m) : 0.f;
             wgt[r * ns + s] = w;
             lsum += ls * w;
         }
@@ -311,20 +363,31 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
         for (int s = lane; s < ns; s += 32) wgt[r * ns + s] *= inv;
     }
     sync();
-    for (int e = tid; e < G * D; e += DM_THREADS) {
-        const int r = e / D, j = e - r * D;
+    // four output dims per thread and pass; the loads of up to MB splits are in flight together
+    constexpr int MB = QREG ? 16 : 8;                // fewer where registers are scarce
+    for (int e = tid; e < G * (D / 4); e += DM_THREADS) {
+        const int r = e / (D / 4), j4 = e - r * (D / 4);
         const size_t row = (size_t)tok * p.n_q + kvh * G + r;
-        const float* pa = p.part_acc + row * ns * D + j;
+        const float4* pa = reinterpret_cast<const float4*>(p.part_acc + row * ns * D) + j4;
         const float* w = wgt + r * ns;
-        float a = 0.f;
-        int s = 0;
-        for (; s + 4 <= ns; s += 4) {
-            const float a0 = __ldcg(pa + (size_t)(s + 0) * D), a1 = __ldcg(pa + (size_t)(s + 1) * D);
-            const float a2 = __ldcg(pa + (size_t)(s + 2) * D), a3 = __ldcg(pa + (size_t)(s + 3) * D);
-            a = fmaf(a0, w[s], a); a = fmaf(a1, w[s + 1], a); a = fmaf(a2, w[s + 2], a); a = fmaf(a3, w[s + 3], a);
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < ns; s0 += MB) {
+            float4 v[MB];
+#pragma unroll
+            for (int u = 0; u < MB; ++u)
+                if (s0 + u < ns) v[u] = __ldcg(pa + (size_t)(s0 + u) * (D / 4));
+#pragma unroll
+            for (int u = 0; u < MB; ++u)
+                if (s0 + u < ns) {
+                    const float ws = w[s0 + u];
+                    a.x = fmaf(v[u].x, ws, a.x); a.y = fmaf(v[u].y, ws, a.y);
+                    a.z = fmaf(v[u].z, ws, a.z); a.w = fmaf(v[u].w, ws, a.w);
+                }
         }
-        for (; s < ns; ++s) a = fmaf(__ldcg(pa + (size_t)s * D), w[s], a);
-        static_cast<__nv_bfloat16*>(p.out)[row * D + j] = __float2bfloat16_rn(a);
+        uint2 o2;
+        *reinterpret_cast<__nv_bfloat162*>(&o2.x) = __floats2bfloat162_rn(a.x, a.y);
+        *reinterpret_cast<__nv_bfloat162*>(&o2.y) = __floats2bfloat162_rn(a.z, a.w);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + row * D + j4 * 4) = o2;
     }
 }
 
