@@ -119,6 +119,68 @@ __global__ void add_rmsnorm_row_kernel(const __nv_bfloat16* __restrict__ delta, 
     }
 }
 
+// The row form for a delta that is float partial sums [n_parts <= 4][rows][H] of a product split
+// over K: every part's loads are issued together with the residual's, and the parts are added in
+// order.
+template <typename TW>
+__global__ void add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, int n_parts, size_t part_stride,
+                                             float* __restrict__ resid, int write_resid, const TW* __restrict__ w, float eps,
+                                             __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const int j = blockIdx.x;
+    const int r = rows ? rows[j] : j;
+    const int i = threadIdx.x * 8;
+    float x[8], wv[8];
+    float ss = 0.f;
+    if (i < H) {
+        float* rrow = resid + (size_t)r * H + i;
+        const float4 r0 = *reinterpret_cast<const float4*>(rrow), r1 = *reinterpret_cast<const float4*>(rrow + 4);
+        float4 d[4][2];
+#pragma unroll
+        for (int pt = 0; pt < 4; ++pt)
+            if (pt < n_parts) {
+                const float* prow = parts + pt * part_stride + (size_t)r * H + i;
+                d[pt][0] = *reinterpret_cast<const float4*>(prow);
+                d[pt][1] = *reinterpret_cast<const float4*>(prow + 4);
+            }
+        if (sizeof(TW) == 2) {
+            const uint4 wr = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + i);
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wr);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { wv[2 * e] = __low2float(w2[e]); wv[2 * e + 1] = __high2float(w2[e]); }
+        } else {
+            const float4 w0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i);
+            const float4 w1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i + 4);
+            wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+        }
+        x[0] = r0.x; x[1] = r0.y; x[2] = r0.z; x[3] = r0.w; x[4] = r1.x; x[5] = r1.y; x[6] = r1.z; x[7] = r1.w;
+        // the residual, then the parts in order: the order of the general kernel
+#pragma unroll
+        for (int pt = 0; pt < 4; ++pt)
+            if (pt < n_parts) {
+                x[0] += d[pt][0].x; x[1] += d[pt][0].y; x[2] += d[pt][0].z; x[3] += d[pt][0].w;
+                x[4] += d[pt][1].x; x[5] += d[pt][1].y; x[6] += d[pt][1].z; x[7] += d[pt][1].w;
+            }
+        if (write_resid) {
+            *reinterpret_cast<float4*>(rrow) = make_float4(x[0], x[1], x[2], x[3]);
+            *reinterpret_cast<float4*>(rrow + 4) = make_float4(x[4], x[5], x[6], x[7]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+    }
+    const float total = block_sum(ss, red);
+    if (i < H) {
+        const float rstd = rsqrtf(total / (float)H + eps);
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(x[2 * e] * rstd * wv[2 * e], x[2 * e + 1] * rstd * wv[2 * e + 1]);
+        *reinterpret_cast<uint4*>(out + (size_t)j * H + i) = o;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // out[m, i] = silu(gu[m, i]) * gu[m, I + i]
 // ---------------------------------------------------------------------------
@@ -295,6 +357,15 @@ extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, l
                           (const bf16*)delta, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
         return launch("add_rmsnorm", add_rmsnorm_row_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
                       (const bf16*)delta, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
+    }
+    if (out_dtype == 1 && delta != nullptr && delta_dtype == 0 && n_parts <= 4 && H % 8 == 0 && H <= 8192 && ps % 4 == 0 &&
+        (uintptr_t)resid % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)delta % 16 == 0) {
+        const int threads = ((H / 8 + 31) / 32) * 32;
+        if (w_dtype == 0)
+            return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<float>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+                          (const float*)delta, n_parts, ps, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
+        return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+                      (const float*)delta, n_parts, ps, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
     }
     if (delta_dtype == 0 && out_dtype == 0)
         return launch_norm<float, float>(delta, n_parts, ps, resid, write_resid, weight, w_dtype, eps, out, rows, n_out, H, stream);

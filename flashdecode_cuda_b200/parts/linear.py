@@ -26,6 +26,7 @@ PROMPT_GEMM = "auto"
 # Up to this many rows the weight-streaming kernel beats the library product (measured on
 # B200 at the sizes of Qwen2.5-1.5B); above it the rows of x no longer fit the registers' reach.
 GEMV_MAX_ROWS = 16
+MAX_PARTS = 4           # most partial sums the norm's fast kernel adds up
 
 
 def fused_prompt_gemm(M: int, N: int, Kd: int) -> bool:
@@ -37,16 +38,24 @@ def fused_prompt_gemm(M: int, N: int, Kd: int) -> bool:
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-           target_ctas: int = 0) -> torch.Tensor:
+           target_ctas: int = 0, parts: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K], w [N, K], bias [N] or None, out [M, N] (dtype of x, or
     float32 for logits).  ``target_ctas``: how many CTAs a decode product
-    should spread over (it splits K inside thread-block clusters to get there)."""
+    should spread over (it splits K to get there).  ``parts``: float32 memory
+    for [splits <= MAX_PARTS, M, N]; when given (no bias) and the product is
+    split, the splits' partial sums are returned in it as [splits, M, N] for the
+    consumer to add up in order (the next norm does), instead of being added
+    inside a thread-block cluster, whose launch and barriers cost more."""
     if x.dtype == torch.float32:
         K.gemm_simt(x, w, bias, out)
         return out
     M, Kd = x.shape
     if M <= GEMV_MAX_ROWS:
         splits = K.gemv_splits(M, w.shape[0], Kd, target_ctas, allow_split=target_ctas > 0)
+        if splits > 1 and parts is not None and bias is None and splits <= MAX_PARTS:
+            view = parts.view(-1)[:splits * M * w.shape[0]].view(splits, M, w.shape[0])
+            K.gemv(x, w, None, view, K.GEMV_PARTIAL, splits)
+            return view
         if splits >= 1:
             K.gemv(x, w, bias, out, K.GEMV_F32 if out.dtype == torch.float32 else K.GEMV_BF16, splits)
             return out

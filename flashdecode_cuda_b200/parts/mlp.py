@@ -10,7 +10,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import FeedForward, Runtime
-from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul
+from .linear import GEMV_MAX_ROWS, MAX_PARTS, fused_prompt_gemm, matmul
 
 
 @register_part("feed_forward", "swiglu")
@@ -59,4 +59,5 @@ class SwiGLU(FeedForward):
             matmul(x, self.w_gate_up, None, gu)
             K.silu_mul(gu, act, tiled=self.tiled)
         out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
-        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count)
+        parts = ws.get("ffn_out_parts", (MAX_PARTS, T, self.hidden_size), torch.float32) if T <= GEMV_MAX_ROWS else None
+        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, parts=parts)

@@ -92,6 +92,29 @@ def test_add_rmsnorm_partial_sums():
     assert rel(out, P.rmsnorm(x, w.double(), 1e-6)) < 1e-5
 
 
+@pytest.mark.parametrize("n_parts,rows,H", [(1, 8, 1536), (2, 3, 200), (4, 16, 8192), (5, 2, 1536), (3, 4, 1537), (4, 5, 8200)])
+def test_add_rmsnorm_partial_sums_to_bfloat16(n_parts, rows, H):
+    """Float partial sums of a split product, bfloat16 output: the row kernel for up to four parts
+    and widths that are multiples of 8 up to 8192, the general kernel otherwise; only chosen rows too."""
+    g = torch.Generator().manual_seed(4)
+    parts = torch.randn(n_parts, rows, H, generator=g).to(DEV)
+    resid = torch.randn(rows, H, generator=g).to(DEV)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16().to(DEV)
+    out = torch.empty(rows, H, dtype=torch.bfloat16, device=DEV)
+    r = resid.clone()
+    K.add_rmsnorm(parts, r, w, 1e-6, out)
+    x = resid.double() + parts.double().sum(0)
+    assert rel(r, x) < 1e-6
+    want = P.rmsnorm(x, w.double(), 1e-6)
+    assert rel(out, want) < 6e-3
+    idx = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=torch.bfloat16, device=DEV)
+    r2 = resid.clone()
+    K.add_rmsnorm(parts, r2, w.float(), 1e-6, out2, rows=idx, write_resid=False)
+    assert torch.equal(r2, resid)
+    assert rel(out2, want[idx.long()]) < 6e-3
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,I", [(3, 176), (65, 8960), (1, 7)])
 def test_silu_mul(dtype, M, I):
@@ -556,10 +579,11 @@ def test_attention_far_key_stands_out(dtype):
 
 @pytest.mark.parametrize("n_q,n_kv,d,bs", [(12, 2, 128, 16), (7, 1, 128, 4), (5, 5, 64, 32), (16, 1, 64, 16),
                                            (28, 4, 128, 16), (40, 8, 128, 8), (3, 3, 128, 1)])
-@pytest.mark.parametrize("n_splits,split_len", [(1, 0), (3, 128), (11, 32)])
+@pytest.mark.parametrize("n_splits,split_len", [(1, 0), (2, 160), (3, 128), (11, 32), (16, 32), (33, 32)])
 def test_attention_decode_tensor_cores(n_q, n_kv, d, bs, n_splits, split_len):
     """The dispatcher's tensor-core kernel for bfloat16 decode steps: groups that
-    are no power of two, cached lengths at tile and split edges, a padding row."""
+    are no power of two, cached lengths at tile and split edges, a padding row.
+    The CTA that finishes last merges the splits and leaves zeros in padding rows."""
     ctx = [0, 15, 16, 17, 127, 128, 300, 63]
     got, want, pad = run_attention("bfloat16", n_q, n_kv, d, bs, ctx=ctx, new=[1] * len(ctx),
                                    n_splits=n_splits, split_len=split_len, pad_rows=1, fn=K.attention)
