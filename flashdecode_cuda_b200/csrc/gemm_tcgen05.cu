@@ -140,6 +140,165 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return d;
 }
 
+// Mode 4: where the token of an output row lives in the cache.
+struct TcToken {
+    int slot, pos;
+    size_t kv_off;
+    bool kv_ok;
+};
+
+__device__ __forceinline__ TcToken tc_token(const TcParams& p, const TcRope& ra, int m) {
+    TcToken t;
+    t.slot = -1; t.pos = 0; t.kv_off = 0; t.kv_ok = false;
+    if (p.mode == 4 && m < p.M) {
+        t.slot = ra.row_slot[ra.tok_row[m]];
+        t.pos = ra.tok_pos[m];
+        if (t.slot >= 0) {
+            if (t.pos < 0 || t.pos >= ra.table_len) {
+                set_status(p.status, STATUS_BAD_POSITION);
+                t.slot = -1;
+            } else if (ra.write_kv) {
+                const int blk = ra.block_table[(size_t)t.slot * ra.max_blocks + t.pos / ra.block_size];
+                if (blk < 0 || blk >= ra.num_blocks) {
+                    set_status(p.status, STATUS_BAD_BLOCK);
+                } else {
+                    t.kv_off = ((size_t)blk * ra.n_kv * ra.block_size + t.pos % ra.block_size) * ra.d;
+                    t.kv_ok = true;
+                }
+            }
+        }
+    }
+    return t;
+}
+
+// The epilogue of 32 consecutive columns n .. n + 31 of output row m, whose float sums are v[0..31].
+__device__ __forceinline__ void tc_store32(const TcParams& p, const TcRope& ra, const TcToken& tk, const uint32_t (&v)[32],
+                                           const int m, const int n) {
+    const int tok_slot = tk.slot, tok_pos = tk.pos;
+    const size_t kv_off = tk.kv_off;
+    const bool kv_ok = tk.kv_ok;
+    if (m >= p.M || n >= p.N) return;
+    if (p.mode == 4) {
+        if (tok_slot < 0) return;                         // padding row or bad position
+        const int d = ra.d, half = d >> 1;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const int col = n + t * 16;                      // first column of this tile of 16
+            if (col >= p.N) break;
+            const int head = col / d, in_head = col - head * d;
+            float lo8[8], hi8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                lo8[j] = __uint_as_float(v[t * 16 + j]);
+                hi8[j] = __uint_as_float(v[t * 16 + 8 + j]);
+            }
+            if (p.bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    lo8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + j]
+                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + j]);
+                    hi8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + 8 + j]
+                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + 8 + j]);
+                }
+            }
+            const bool is_v = head >= ra.n_q + ra.n_kv;
+            int j_lo, j_hi;                                   // dims of the two groups of 8 inside the head
+            if (is_v) {
+                j_lo = in_head; j_hi = in_head + 8;
+            } else {
+                j_lo = (in_head >> 4) * 8; j_hi = j_lo + half;
+                const float4* c4 = reinterpret_cast<const float4*>(ra.cos_t + (size_t)tok_pos * half + j_lo);
+                const float4* s4 = reinterpret_cast<const float4*>(ra.sin_t + (size_t)tok_pos * half + j_lo);
+                const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+                const float cs[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+                const float sn[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float x1 = lo8[j], x2 = hi8[j];
+                    lo8[j] = x1 * cs[j] - x2 * sn[j];
+                    hi8[j] = x2 * cs[j] + x1 * sn[j];
+                }
+            }
+            uint32_t pl[4], ph[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 a = __floats2bfloat162_rn(lo8[2 * j], lo8[2 * j + 1]);
+                const __nv_bfloat162 b = __floats2bfloat162_rn(hi8[2 * j], hi8[2 * j + 1]);
+                pl[j] = *reinterpret_cast<const uint32_t*>(&a);
+                ph[j] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+            __nv_bfloat16* dst;
+            if (head < ra.n_q) {
+                dst = static_cast<__nv_bfloat16*>(p.out) + ((size_t)m * ra.n_q + head) * d;
+            } else {
+                if (!kv_ok) continue;
+                const int kvh = is_v ? head - ra.n_q - ra.n_kv : head - ra.n_q;
+                dst = (is_v ? ra.v_pool : ra.k_pool) + kv_off + (size_t)kvh * ra.block_size * d;
+            }
+            *reinterpret_cast<uint4*>(dst + j_lo) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+            *reinterpret_cast<uint4*>(dst + j_hi) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+        }
+        return;
+    }
+    if (p.mode == 3) {
+        // 32 columns = two tiles of 8 gate + 8 up values -> 16 outputs (N is a multiple of 16)
+        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * (p.N >> 1) + (n >> 1);
+        uint32_t packed[8];
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                const float g0 = __uint_as_float(v[t * 16 + j]), u0 = __uint_as_float(v[t * 16 + 8 + j]);
+                const float g1 = __uint_as_float(v[t * 16 + j + 1]), u1 = __uint_as_float(v[t * 16 + 9 + j]);
+                const __nv_bfloat162 r = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0,
+                                                               g1 / (1.f + __expf(-g1)) * u1);
+                packed[t * 4 + (j >> 1)] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+        *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        if (n + 16 < p.N) *reinterpret_cast<uint4*>(o + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        return;
+    }
+    const int cols = min(32, p.N - n);
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+    if (p.bias != nullptr) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const int nn = min(n + j, p.N - 1);
+            f[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[nn]
+                               : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[nn]);
+        }
+    }
+    if (p.mode == 1) {
+        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n;
+        if (cols == 32 && (p.N & 7) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                const __nv_bfloat162 r0 = __floats2bfloat162_rn(f[j], f[j + 1]), r1 = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
+                const __nv_bfloat162 r2 = __floats2bfloat162_rn(f[j + 4], f[j + 5]), r3 = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(*reinterpret_cast<const uint32_t*>(&r0), *reinterpret_cast<const uint32_t*>(&r1),
+                                                              *reinterpret_cast<const uint32_t*>(&r2), *reinterpret_cast<const uint32_t*>(&r3));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < cols) o[j] = __float2bfloat16_rn(f[j]);
+        }
+    } else {
+        float* o = static_cast<float*>(p.out) + (size_t)m * p.N + n;
+        if (cols == 32 && (p.N & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < cols) o[j] = f[j];
+        }
+    }
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     const TcParams p, const TcRope ra) {
@@ -218,155 +377,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // all lanes of a warp must agree before the warp-wide tensor-memory loads
         const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&bars[2 * TC_STAGES]), 0, abort_flag, p.status));
         tc_fence_after();
-        // mode 4: where this thread's token lives
-        int tok_slot = -1, tok_pos = 0;
-        size_t kv_off = 0;
-        bool kv_ok = false;
-        if (p.mode == 4 && m < p.M) {
-            tok_slot = ra.row_slot[ra.tok_row[m]];
-            tok_pos = ra.tok_pos[m];
-            if (tok_slot >= 0) {
-                if (tok_pos < 0 || tok_pos >= ra.table_len) {
-                    set_status(p.status, STATUS_BAD_POSITION);
-                    tok_slot = -1;
-                } else if (ra.write_kv) {
-                    const int blk = ra.block_table[(size_t)tok_slot * ra.max_blocks + tok_pos / ra.block_size];
-                    if (blk < 0 || blk >= ra.num_blocks) {
-                        set_status(p.status, STATUS_BAD_BLOCK);
-                    } else {
-                        kv_off = ((size_t)blk * ra.n_kv * ra.block_size + tok_pos % ra.block_size) * ra.d;
-                        kv_ok = true;
-                    }
-                }
-            }
-        }
+        const TcToken tk = tc_token(p, ra, m);
         if (ok) {
 #pragma unroll 1
             for (int c0 = 0; c0 < TC_BN; c0 += 32) {
                 uint32_t v[32];
                 tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + c0, v);
                 tc_wait_ld();
-                const int n = n0 + c0;
-                if (m >= p.M || n >= p.N) continue;
-                if (p.mode == 4) {
-                    if (tok_slot < 0) continue;                       // padding row or bad position
-                    const int d = ra.d, half = d >> 1;
-#pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        const int col = n + t * 16;                      // first column of this tile of 16
-                        if (col >= p.N) break;
-                        const int head = col / d, in_head = col - head * d;
-                        float lo8[8], hi8[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            lo8[j] = __uint_as_float(v[t * 16 + j]);
-                            hi8[j] = __uint_as_float(v[t * 16 + 8 + j]);
-                        }
-                        if (p.bias != nullptr) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                lo8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + j]
-                                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + j]);
-                                hi8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + 8 + j]
-                                                     : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + 8 + j]);
-                            }
-                        }
-                        const bool is_v = head >= ra.n_q + ra.n_kv;
-                        int j_lo, j_hi;                                   // dims of the two groups of 8 inside the head
-                        if (is_v) {
-                            j_lo = in_head; j_hi = in_head + 8;
-                        } else {
-                            j_lo = (in_head >> 4) * 8; j_hi = j_lo + half;
-                            const float4* c4 = reinterpret_cast<const float4*>(ra.cos_t + (size_t)tok_pos * half + j_lo);
-                            const float4* s4 = reinterpret_cast<const float4*>(ra.sin_t + (size_t)tok_pos * half + j_lo);
-                            const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
-                            const float cs[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
-                            const float sn[8] = {sa.x, sa.y, sa.z, sa.w, sb.x, sb.y, sb.z, sb.w};
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float x1 = lo8[j], x2 = hi8[j];
-                                lo8[j] = x1 * cs[j] - x2 * sn[j];
-                                hi8[j] = x2 * cs[j] + x1 * sn[j];
-                            }
-                        }
-                        uint32_t pl[4], ph[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const __nv_bfloat162 a = __floats2bfloat162_rn(lo8[2 * j], lo8[2 * j + 1]);
-                            const __nv_bfloat162 b = __floats2bfloat162_rn(hi8[2 * j], hi8[2 * j + 1]);
-                            pl[j] = *reinterpret_cast<const uint32_t*>(&a);
-                            ph[j] = *reinterpret_cast<const uint32_t*>(&b);
-                        }
-                        __nv_bfloat16* dst;
-                        if (head < ra.n_q) {
-                            dst = static_cast<__nv_bfloat16*>(p.out) + ((size_t)m * ra.n_q + head) * d;
-                        } else {
-                            if (!kv_ok) continue;
-                            const int kvh = is_v ? head - ra.n_q - ra.n_kv : head - ra.n_q;
-                            dst = (is_v ? ra.v_pool : ra.k_pool) + kv_off + (size_t)kvh * ra.block_size * d;
-                        }
-                        *reinterpret_cast<uint4*>(dst + j_lo) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-                        *reinterpret_cast<uint4*>(dst + j_hi) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                    }
-                    continue;
-                }
-                if (p.mode == 3) {
-                    // 32 columns = two tiles of 8 gate + 8 up values -> 16 outputs (N is a multiple of 16)
-                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * (p.N >> 1) + (n >> 1);
-                    uint32_t packed[8];
-#pragma unroll
-                    for (int t = 0; t < 2; ++t)
-#pragma unroll
-                        for (int j = 0; j < 8; j += 2) {
-                            const float g0 = __uint_as_float(v[t * 16 + j]), u0 = __uint_as_float(v[t * 16 + 8 + j]);
-                            const float g1 = __uint_as_float(v[t * 16 + j + 1]), u1 = __uint_as_float(v[t * 16 + 9 + j]);
-                            const __nv_bfloat162 r = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0,
-                                                                           g1 / (1.f + __expf(-g1)) * u1);
-                            packed[t * 4 + (j >> 1)] = *reinterpret_cast<const uint32_t*>(&r);
-                        }
-                    *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    if (n + 16 < p.N) *reinterpret_cast<uint4*>(o + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    continue;
-                }
-                const int cols = min(32, p.N - n);
-                float f[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-                if (p.bias != nullptr) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int nn = min(n + j, p.N - 1);
-                        f[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[nn]
-                                           : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[nn]);
-                    }
-                }
-                if (p.mode == 1) {
-                    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n;
-                    if (cols == 32 && (p.N & 7) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            const __nv_bfloat162 r0 = __floats2bfloat162_rn(f[j], f[j + 1]), r1 = __floats2bfloat162_rn(f[j + 2], f[j + 3]);
-                            const __nv_bfloat162 r2 = __floats2bfloat162_rn(f[j + 4], f[j + 5]), r3 = __floats2bfloat162_rn(f[j + 6], f[j + 7]);
-                            *reinterpret_cast<uint4*>(o + j) = make_uint4(*reinterpret_cast<const uint32_t*>(&r0), *reinterpret_cast<const uint32_t*>(&r1),
-                                                                          *reinterpret_cast<const uint32_t*>(&r2), *reinterpret_cast<const uint32_t*>(&r3));
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < cols) o[j] = __float2bfloat16_rn(f[j]);
-                    }
-                } else {
-                    float* o = static_cast<float*>(p.out) + (size_t)m * p.N + n;
-                    if (cols == 32 && (p.N & 3) == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4*>(o + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < cols) o[j] = f[j];
-                    }
-                }
+                tc_store32(p, ra, tk, v, m, n0 + c0);
             }
         }
     }
@@ -375,6 +393,143 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
+    }
+}
+
+// ---- the wide, persistent form --------------------------------------------
+// 128 x 256 tiles, one CTA per SM that walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...:
+//  * a 128 x 128 tile reads 32 KB of shared memory for every 2 MFLOP, which is the whole
+//    shared-memory bandwidth of an SM at the tensor cores' rate; 128 x 256 reads 48 KB for 4 MFLOP;
+//  * the accumulator is double-buffered in tensor memory (2 x 256 of the 512 columns): the
+//    epilogue warps drain one tile while the MMA warp fills the next, and the TMA warp runs
+//    ahead across tile boundaries, four stages of 48 KB deep;
+//  * consecutive tiles share their W panel (tile index = n_tile * tiles_m + m_tile), so the CTAs
+//    running at one time read the same few panels of W through L2.
+constexpr int TW_BN = 256, TW_STAGES = 4;
+constexpr int TW_B_BYTES = TW_BN * TC_BK * 2;                 // 32 KB
+constexpr int TW_STAGE_BYTES = TC_A_BYTES + TW_B_BYTES;       // 48 KB
+constexpr int TW_SMEM = TW_STAGES * TW_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int TW_EPI_WARPS = 8;               // two per quarter of the tensor-memory lanes, 128 columns each
+constexpr int TW_THREADS = (2 + TW_EPI_WARPS) * 32;
+
+__global__ void __launch_bounds__(TW_THREADS, 1)
+gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         const TcParams p, const TcRope ra, const int tiles_m, const int tiles_n) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TW_STAGES * TW_STAGE_BYTES);
+    uint64_t* full = bars;                       // [S] a stage has landed
+    uint64_t* empty = bars + TW_STAGES;          // [S] the MMAs that read a stage are done
+    uint64_t* acc_full = bars + 2 * TW_STAGES;   // [2] an accumulator is complete
+    uint64_t* acc_empty = acc_full + 2;          // [2] the epilogue has read it (one arrival per epilogue warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag[0] = 0;
+        abort_flag[1] = 0;
+        for (int s = 0; s < TW_STAGES; ++s) {
+            mbar_init(s_addr(&full[s]), 1);
+            mbar_init(s_addr(&empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_addr(&acc_full[b]), 1);
+            mbar_init(s_addr(&acc_empty[b]), TW_EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer ----
+        int it = 0;                                    // k-blocks issued so far, over all tiles
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TW_BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % TW_STAGES;
+                if (it >= TW_STAGES && !mbar_wait(s_addr(&empty[s]), ((it / TW_STAGES) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                if (*abort_flag) { ok = false; break; }
+                const uint32_t fb = s_addr(&full[s]);
+                mbar_expect_tx(fb, TW_STAGE_BYTES);
+                unsigned char* a = tiles + s * TW_STAGE_BYTES;
+                tma_load_2d(s_addr(a), &map_x, fb, k * TC_BK, m0);
+                tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);                       // W rows n0 .. n0 + 127
+                tma_load_2d(s_addr(a + TC_A_BYTES + TC_B_BYTES), &map_w, fb, k * TC_BK, n0 + TC_BN);  // and the next 128
+            }
+        }
+        if (*abort_flag) {
+            for (int j = max(0, it - TW_STAGES); j < it; ++j)
+                mbar_wait(s_addr(&full[j % TW_STAGES]), (j / TW_STAGES) & 1, abort_flag + 1, nullptr);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TW_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        int it = 0, t = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++t) {
+            const int buf = t & 1;
+            if (t >= 2 && !mbar_wait(s_addr(&acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status)) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + buf * TW_BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % TW_STAGES;
+                if (!mbar_wait(s_addr(&full[s]), (it / TW_STAGES) & 1, abort_flag, p.status)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a = s_addr(tiles + s * TW_STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)
+                    tc_mma(acc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0);
+                tc_commit(s_addr(&empty[s]));
+            }
+            if (ok) tc_commit(s_addr(&acc_full[buf]));
+        }
+        if (!ok || *abort_flag) { tc_commit(s_addr(&acc_full[0])); tc_commit(s_addr(&acc_full[1])); }
+    } else if (warp >= 2) {
+        // ---- epilogue: warp w reads lanes 32 (w % 4) .. + 32; warps 2-5 take columns 0..127, 6-9 the rest ----
+        const int quarter = warp & 3;
+        const int col_half = (warp - 2) >> 2;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        int t = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
+            const int buf = t & 1;
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TW_BN;
+            const int m = m0 + quarter * 32 + lane;
+            const TcToken tk = tc_token(p, ra, m);
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status)) &&
+                            *abort_flag == 0;
+            if (!__all_sync(0xffffffffu, ok)) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = col_half * (TW_BN / 2); c0 < (col_half + 1) * (TW_BN / 2); c0 += 32) {
+                uint32_t v[32];
+                tc_ld32(tmem + lane_base + buf * TW_BN + c0, v);
+                tc_wait_ld();
+                tc_store32(p, ra, tk, v, m, n0 + c0);
+            }
+            // the accumulator may be overwritten once all epilogue warps have read it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_addr(&acc_empty[buf])) : "memory");
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
 }
 
@@ -424,9 +579,46 @@ static int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out) {
     return 0;
 }
 
+int g_tc_wide = 1;      // 1: the wide persistent kernel where N >= 256; 0: always 128 x 128 tiles, one per CTA
+
+static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcParams& p, const TcRope& ra, cudaStream_t stream,
+                     const char* what) {
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TW_SMEM);
+        if (e != cudaSuccess) return fail(-3, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", TW_SMEM, cudaGetErrorString(e));
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        configured = true;
+    }
+    const int tiles_m = (p.M + TC_BM - 1) / TC_BM;
+    if (g_tc_wide && p.N >= TW_BN) {
+        const int tiles_n = (p.N + TW_BN - 1) / TW_BN;
+        const long long n_tiles = (long long)tiles_m * tiles_n;
+        FD_REQUIRE(n_tiles < (1ll << 30), -2, "gemm_tcgen05: %lld tiles", n_tiles);
+        const int grid = (int)(n_tiles < sms ? n_tiles : sms);
+        gemm_tcgen05_wide_kernel<<<grid, TW_THREADS, TW_SMEM, stream>>>(mx, mw, p, ra, tiles_m, tiles_n);
+        return check_launch(what);
+    }
+    dim3 grid((p.N + TC_BN - 1) / TC_BN, tiles_m);
+    FD_REQUIRE(grid.y <= 65535, -2, "gemm_tcgen05: M=%d too large for one launch", p.M);
+    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(mx, mw, p, ra);
+    return check_launch(what);
+}
+
 }  // namespace fd
 
 using namespace fd;
+
+// Which tiling the products use from now on (1: wide persistent kernel where N >= 256, the default;
+// 0: 128 x 128 tiles only).  For tests and measurements.
+extern "C" int fd_gemm_tc_set_wide(int on) {
+    g_tc_wide = on ? 1 : 0;
+    return 0;
+}
 
 // 1 if the tensor-core product takes these sizes (K a multiple of 8, enough rows to be worth a
 // 128-row tile), else 0.
@@ -449,19 +641,10 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
     if (rc != 0) return rc;
     rc = tensor_map(w, N, K, &mw);
     if (rc != 0) return rc;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        if (e != cudaSuccess) return fail(-3, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", TC_SMEM, cudaGetErrorString(e));
-        configured = true;
-    }
     TcParams p;
     p.bias = bias; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = bias_f32;
-    dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
-    FD_REQUIRE(grid.y <= 65535, -2, "gemm_tcgen05: M=%d too large for one launch", M);
     TcRope ra = {};
-    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(mx, mw, p, ra);
-    return check_launch("gemm_tcgen05");
+    return launch_tc(mx, mw, p, ra, stream, "gemm_tcgen05");
 }
 
 // The q/k/v projection of a prompt step with bias, rotary encoding and the append to the
@@ -484,12 +667,6 @@ extern "C" int fd_gemm_tc_qkv_rope(const void* x, const void* w, const void* bia
     if (rc != 0) return rc;
     rc = tensor_map(w, N, K, &mw);
     if (rc != 0) return rc;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        if (e != cudaSuccess) return fail(-3, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", TC_SMEM, cudaGetErrorString(e));
-        configured = true;
-    }
     TcParams p;
     p.bias = bias; p.out = q_out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = 4; p.bias_f32 = bias_f32;
     TcRope ra;
@@ -497,8 +674,5 @@ extern "C" int fd_gemm_tc_qkv_rope(const void* x, const void* w, const void* bia
     ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool; ra.block_table = block_table;
     ra.table_len = table_len; ra.max_blocks = max_blocks; ra.num_blocks = num_blocks; ra.block_size = block_size;
     ra.n_q = n_q; ra.n_kv = n_kv; ra.d = d; ra.write_kv = write_kv;
-    dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
-    FD_REQUIRE(grid.y <= 65535, -2, "gemm_tcgen05: M=%d too large for one launch", M);
-    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM, stream>>>(mx, mw, p, ra);
-    return check_launch("gemm_tc_qkv_rope");
+    return launch_tc(mx, mw, p, ra, stream, "gemm_tc_qkv_rope");
 }

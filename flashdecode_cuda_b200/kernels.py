@@ -81,6 +81,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_rope_append": [P, I, I, LL, P, I, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
         "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemm_tc_supported": [I, I, I],
+        "fd_gemm_tc_set_wide": [I],
         "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
         "fd_gemm_tc_qkv_rope": [P, P, P, I, P, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemv_splits": [I, I, I, I, I],
@@ -239,6 +240,13 @@ def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
 
 
 GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
+
+
+def gemm_tc_set_wide(on: bool) -> None:
+    """Which tiling ``gemm_tc`` and ``gemm_tc_qkv_rope`` use from now on: the persistent kernel with
+    128 x 256 tiles and a double-buffered accumulator where N >= 256 (the default), or 128 x 128
+    tiles, one per CTA, everywhere.  For tests and measurements."""
+    lib().fd_gemm_tc_set_wide(int(on))
 
 
 def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,

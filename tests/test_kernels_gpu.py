@@ -201,11 +201,20 @@ def test_gemv_refuses_what_it_cannot_do():
                torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV), K.GEMV_BF16)
 
 
+@pytest.fixture(params=[True, False], ids=["wide", "square"])
+def tc_tiling(request):
+    """Both tilings of the tcgen05 product: 128 x 256 persistent (N >= 256) and 128 x 128."""
+    K.gemm_tc_set_wide(request.param)
+    yield request.param
+    K.gemm_tc_set_wide(True)
+
+
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (128, 256, 256), (130, 200, 72), (70, 333, 1536), (2048, 2048, 1536),
-                                    (300, 1536, 8960), (17, 16, 8)])
-def test_gemm_tcgen05(M, N, K_):
+                                    (300, 1536, 8960), (17, 16, 8), (1000, 384, 136), (4096, 4864, 256), (129, 257, 64)])
+def test_gemm_tcgen05(M, N, K_, tc_tiling):
     """The TMA + tcgen05 product of prompt steps: full tiles, ragged edges in M, N
-    and K (zero-filled by TMA), bias in either dtype, float output."""
+    and K (zero-filled by TMA), more tiles than SMs (the persistent kernel walks several,
+    alternating its two accumulators), bias in either dtype, float output."""
     g = torch.Generator().manual_seed(M + N)
     x = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16).to(DEV)
@@ -423,7 +432,7 @@ def test_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,bs,Kd", [(12, 2, 128, 16, 1536), (6, 2, 48, 4, 96), (5, 1, 64, 32, 72)])
-def test_prompt_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd):
+def test_prompt_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, tc_tiling):
     """The tcgen05 q/k/v projection over two prompts (several 128-row tiles, a
     ragged last one), one of them continuing a cached prefix, plus a padding row."""
     g = torch.Generator().manual_seed(n_q)
