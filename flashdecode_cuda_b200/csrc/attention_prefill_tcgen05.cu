@@ -4,20 +4,22 @@
 // one query head and walks the keys in tiles of 64:
 //
 //   S[128 q, 64 keys] = Q K^T      tcgen05.mma, both operands K-major in shared memory,
-//                                  accumulator S in tensor memory (64 columns)
+//                                  accumulator S in tensor memory (two tiles of 64 columns: the
+//                                  next tile's scores are computed while the softmax works)
 //   softmax                        4 warps, one thread per query row: tcgen05.ld of its S row,
 //                                  running max / sum in float (base 2), P written to shared
 //                                  memory as bfloat16 in the 128-byte-swizzled K-major layout
 //   O[128 q, 128 d] += P V         tcgen05.mma with V as an MN-major operand (V rows are keys,
 //                                  the head dimension is contiguous), accumulator O in tensor
 //                                  memory (128 more columns), rescaled in place when a row's
-//                                  maximum moved
+//                                  maximum grew by more than 2^8
 //
 // Keys and values come straight from the paged pools by TMA: one 2-D box of
 // (block_size keys x 64 dims) per cache block and half head, placed so that a
-// tile of 64 keys forms the canonical swizzled layout.  Roles: warp 0 issues
-// TMA, warp 1 issues MMAs and owns the tensor-memory allocation, warps 2-5 do
-// the softmax and the epilogue.  Every mbarrier wait is bounded in time; a wait
+// tile of 64 keys forms the canonical swizzled layout; four tiles are in
+// flight.  Roles: warp 0 issues TMA (the copies of a tile from as many lanes at
+// once, the block numbers fetched 32 at a time ahead of use), warp 1 issues MMAs
+// and owns the tensor-memory allocation, warps 2-5 do the softmax and the epilogue.  Every mbarrier wait is bounded in time; a wait
 // that runs out sets a status bit and the CTA winds down (see gemm_tcgen05.cu).
 #include <cuda.h>
 #include <math.h>
@@ -33,15 +35,15 @@ namespace fd {
 constexpr int TA_D = 128;                 // head size
 constexpr int TA_BM = 128;                // queries per CTA
 constexpr int TA_BN = 64;                 // keys per tile
-constexpr int TA_STAGES = 2;              // key/value tiles in flight
+constexpr int TA_STAGES = 4;              // key/value tiles in flight
 constexpr int TA_THREADS = 192;
 constexpr int TA_QSLAB = TA_BM * 128;     // bytes of a [128 queries][64 bf16] slab (Q: two of them; P: one)
 constexpr int TA_KSLAB = TA_BN * 128;     // bytes of a [64 keys][64 bf16] slab (K and V: two each)
 constexpr int TA_QTILE = 2 * TA_QSLAB;    // Q [128][128]
 constexpr int TA_PTILE = TA_QSLAB;        // P [128][64]
 constexpr int TA_KTILE = 2 * TA_KSLAB;    // K or V [64][128]
-// 112 KB + barriers: two CTAs share an SM (and its 512 tensor-memory columns, 256 each), so one
-// CTA's softmax runs under the other's matrix products
+// 176 KB + barriers, one CTA per SM: four key/value tiles in flight hide the copies' latency (measured:
+// better than two CTAs per SM with two tiles each, 54 against 69 us for a 2,048-token prompt)
 constexpr int TA_SMEM = TA_QTILE + TA_PTILE + TA_STAGES * 2 * TA_KTILE + 128;
 constexpr unsigned long long TA_WAIT_NS = 200ull * 1000 * 1000;
 
@@ -133,7 +135,7 @@ __device__ __forceinline__ uint64_t ta_desc_mn(uint32_t addr, uint32_t slab_byte
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-__global__ void __launch_bounds__(TA_THREADS, 2)
+__global__ void __launch_bounds__(TA_THREADS, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ __align__(1024) unsigned char ta_raw[];
@@ -196,7 +198,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t tmem_s = tmem, tmem_o = tmem + 128;       // columns 0..63 and 64..127: two S tiles, 128..255: O
 
     if (warp == 0) {
-        // ---- TMA producer: lane 0 issues the copies; the warp's lanes fetch the block numbers of the
+        // ---- TMA producer: the warp's lanes fetch the block numbers of the
         // next 32 copies together, one chunk ahead, so that no copy waits for a table entry ----
         if (lane == 0) {
             ta_expect(ta_saddr(&bars[0]), TA_QTILE);
@@ -229,19 +231,19 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             unsigned char* ks = kv_s + s * 2 * TA_KTILE;
             unsigned char* vs = ks + TA_KTILE;
             const int t0 = t_begin + it * TA_BN;
-            for (int j = 0; j < per_tile; ++j) {
-                const int g = it * per_tile + j;
-                if ((g & 31) == 0) { blk_cur = blk_next; blk_next = fetch(g + 32 + lane); }
-                const int blk = __shfl_sync(0xffffffffu, blk_cur, g & 31);
-                if (lane == 0) {
-                    // row of the pool seen as [rows, d]: the (block, head) slab, and the tile's place in a larger block
-                    const int r0 = j * box;
-                    const int row = (blk * p.n_kv + kvh) * bs + (t0 + r0) % bs;
-                    ta_tma(ta_saddr(ks + r0 * 128), &map_k, full, 0, row);
-                    ta_tma(ta_saddr(ks + TA_KSLAB + r0 * 128), &map_k, full, 64, row);
-                    ta_tma(ta_saddr(vs + r0 * 128), &map_v, full, 0, row);
-                    ta_tma(ta_saddr(vs + TA_KSLAB + r0 * 128), &map_v, full, 64, row);
-                }
+            // The tile's copies (4 per cache block: K and V, each in two halves of the head) are issued by as
+            // many lanes at once: one lane issuing them one after another took longer than the tile's tensor work.
+            const int g0 = it * per_tile;                      // the tile's first copy group; chunks of 32 start on a tile
+            if ((g0 & 31) == 0) { blk_cur = blk_next; blk_next = fetch(g0 + 32 + lane); }
+            __syncwarp();                                      // the expectation is set before any copy can complete
+            const int j = lane >> 2, part = lane & 3;
+            const int blk = __shfl_sync(0xffffffffu, blk_cur, (g0 + j) & 31);
+            if (j < per_tile) {
+                // row of the pool seen as [rows, d]: the (block, head) slab, and the tile's place in a larger block
+                const int r0 = j * box;
+                const int row = (blk * p.n_kv + kvh) * bs + (t0 + r0) % bs;
+                unsigned char* dst = ((part & 2) ? vs : ks) + (part & 1) * TA_KSLAB + r0 * 128;
+                ta_tma(ta_saddr(dst), (part & 2) ? &map_v : &map_k, full, (part & 1) * 64, row);
             }
             issued = it + 1;
         }
@@ -318,9 +320,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (!(t >= lo && t < hi && t <= pos && (p.window <= 0 || pos - t < p.window))) x[j] = -INFINITY;
                 }
             }
-            float mx = x[0];
+            float mx4[4] = {x[0], x[1], x[2], x[3]};          // four chains instead of one of 63 dependent steps
 #pragma unroll
-            for (int j = 1; j < TA_BN; ++j) mx = fmaxf(mx, x[j]);
+            for (int j = 4; j < TA_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], x[j]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // The maximum moves only when it grows by more than 2^8 (P stays below 256, exact enough in
             // bfloat16 and far from overflow in the 32-bit sums): most tiles then need no rescaling of O
             float m_new = fmaxf(m_run, mx);
@@ -328,17 +331,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float alpha = m_new == m_run ? 1.f : ta_ex2((m_run - m_new) * scale_log2);   // m_run = -inf: 0
             m_run = m_new;
             const float m_off = m_new == -INFINITY ? 0.f : m_new * scale_log2;
-            float rs = 0.f;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t packed[TA_BN / 2];
 #pragma unroll
             for (int j = 0; j < TA_BN; j += 2) {
                 const float p0 = ta_ex2(fmaf(x[j], scale_log2, -m_off));
                 const float p1 = ta_ex2(fmaf(x[j + 1], scale_log2, -m_off));
-                rs += p0 + p1;
+                rs4[(j >> 1) & 3] += p0 + p1;
                 const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
                 packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
             }
-            l_run = l_run * alpha + rs;
+            l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
             // The previous P V must be complete before P is overwritten and before O is touched;
             // then O *= alpha where a maximum moved
             if (it > 0) {
@@ -484,3 +487,4 @@ int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_
 }
 
 }  // namespace fd
+
