@@ -465,8 +465,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 mbar_expect_tx(fb, TW_STAGE_BYTES);
                 unsigned char* a = tiles + s * TW_STAGE_BYTES;
                 tma_load_2d(s_addr(a), &map_x, fb, k * TC_BK, m0);
-                tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);                       // W rows n0 .. n0 + 127
-                tma_load_2d(s_addr(a + TC_A_BYTES + TC_B_BYTES), &map_w, fb, k * TC_BK, n0 + TC_BN);  // and the next 128
+                tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);     // 256 rows of W in one box
             }
         }
         if (*abort_flag) {
@@ -552,21 +551,21 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Tensor map of a row-major bf16 matrix [rows, cols] read in boxes of 128 rows x 64 columns
+// Tensor map of a row-major bf16 matrix [rows, cols] read in boxes of box_rows (128 or 256) rows x 64 columns
 // with the 128-byte swizzle.  Maps are cached by (address, shape): weights and workspace
 // buffers keep their addresses.
-static int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out) {
-    static std::map<std::tuple<const void*, int, int>, CUtensorMap> cache;
+static int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out, int box_rows = TC_BM) {
+    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
-    auto key = std::make_tuple(ptr, rows, cols);
+    auto key = std::make_tuple(ptr, rows, cols, box_rows);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return 0; }
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return fail(-4, "gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)TC_BM};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
     CUtensorMap m;
     CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
@@ -581,7 +580,7 @@ static int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out) {
 
 int g_tc_wide = 1;      // 1: the wide persistent kernel where N >= 256; 0: always 128 x 128 tiles, one per CTA
 
-static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcParams& p, const TcRope& ra, cudaStream_t stream,
+static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRope& ra, cudaStream_t stream,
                      const char* what) {
     static bool configured = false;
     static int sms = 0;
@@ -595,7 +594,13 @@ static int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const TcParam
         configured = true;
     }
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM;
-    if (g_tc_wide && p.N >= TW_BN) {
+    const bool wide = g_tc_wide && p.N >= TW_BN;
+    CUtensorMap mx, mw;
+    int rc = tensor_map(x, p.M, p.K, &mx);
+    if (rc != 0) return rc;
+    rc = tensor_map(w, p.N, p.K, &mw, wide ? TW_BN : TC_BM);
+    if (rc != 0) return rc;
+    if (wide) {
         const int tiles_n = (p.N + TW_BN - 1) / TW_BN;
         const long long n_tiles = (long long)tiles_m * tiles_n;
         FD_REQUIRE(n_tiles < (1ll << 30), -2, "gemm_tcgen05: %lld tiles", n_tiles);
@@ -636,15 +641,10 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
     FD_REQUIRE(mode != 3 || N % 16 == 0, -2, "gemm_tcgen05: the gated form needs N (= 2 x outputs) to be a multiple of 16, got %d", N);
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0, -2,
                "gemm_tcgen05: x, W and out must be 16-byte aligned");
-    CUtensorMap mx, mw;
-    int rc = tensor_map(x, M, K, &mx);
-    if (rc != 0) return rc;
-    rc = tensor_map(w, N, K, &mw);
-    if (rc != 0) return rc;
     TcParams p;
     p.bias = bias; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = bias_f32;
     TcRope ra = {};
-    return launch_tc(mx, mw, p, ra, stream, "gemm_tcgen05");
+    return launch_tc(x, w, p, ra, stream, "gemm_tcgen05");
 }
 
 // The q/k/v projection of a prompt step with bias, rotary encoding and the append to the
@@ -662,11 +662,6 @@ extern "C" int fd_gemm_tc_qkv_rope(const void* x, const void* w, const void* bia
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
                (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 && (uintptr_t)cos_t % 16 == 0 &&
                (uintptr_t)sin_t % 16 == 0, -2, "gemm_tc_qkv_rope: all arrays must be 16-byte aligned");
-    CUtensorMap mx, mw;
-    int rc = tensor_map(x, M, K, &mx);
-    if (rc != 0) return rc;
-    rc = tensor_map(w, N, K, &mw);
-    if (rc != 0) return rc;
     TcParams p;
     p.bias = bias; p.out = q_out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = 4; p.bias_f32 = bias_f32;
     TcRope ra;
@@ -674,5 +669,5 @@ extern "C" int fd_gemm_tc_qkv_rope(const void* x, const void* w, const void* bia
     ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool; ra.block_table = block_table;
     ra.table_len = table_len; ra.max_blocks = max_blocks; ra.num_blocks = num_blocks; ra.block_size = block_size;
     ra.n_q = n_q; ra.n_kv = n_kv; ra.d = d; ra.write_kv = write_kv;
-    return launch_tc(mx, mw, p, ra, stream, "gemm_tc_qkv_rope");
+    return launch_tc(x, w, p, ra, stream, "gemm_tc_qkv_rope");
 }
