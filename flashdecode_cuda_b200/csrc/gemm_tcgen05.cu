@@ -193,12 +193,24 @@ __device__ __forceinline__ void tc_store32(const TcParams& p, const TcRope& ra, 
                 hi8[j] = __uint_as_float(v[t * 16 + 8 + j]);
             }
             if (p.bias != nullptr) {
+                // the 16 bias values of the tile with vector loads (col is a multiple of 16, the launcher checks the base)
+                if (p.bias_f32) {
+                    const float4* b4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.bias) + col);
+                    const float4 b0 = b4[0], b1 = b4[1], b2 = b4[2], b3 = b4[3];
+                    lo8[0] += b0.x; lo8[1] += b0.y; lo8[2] += b0.z; lo8[3] += b0.w;
+                    lo8[4] += b1.x; lo8[5] += b1.y; lo8[6] += b1.z; lo8[7] += b1.w;
+                    hi8[0] += b2.x; hi8[1] += b2.y; hi8[2] += b2.z; hi8[3] += b2.w;
+                    hi8[4] += b3.x; hi8[5] += b3.y; hi8[6] += b3.z; hi8[7] += b3.w;
+                } else {
+                    const uint4* b4 = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.bias) + col);
+                    const uint4 bl = b4[0], bh = b4[1];
+                    const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&bl);
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&bh);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    lo8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + j]
-                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + j]);
-                    hi8[j] += p.bias_f32 ? static_cast<const float*>(p.bias)[col + 8 + j]
-                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[col + 8 + j]);
+                    for (int j = 0; j < 4; ++j) {
+                        lo8[2 * j] += __low2float(l2[j]); lo8[2 * j + 1] += __high2float(l2[j]);
+                        hi8[2 * j] += __low2float(h2[j]); hi8[2 * j + 1] += __high2float(h2[j]);
+                    }
                 }
             }
             const bool is_v = head >= ra.n_q + ra.n_kv;
@@ -661,7 +673,7 @@ extern "C" int fd_gemm_tc_qkv_rope(const void* x, const void* w, const void* bia
     FD_REQUIRE(d >= 16 && d % 16 == 0, -2, "gemm_tc_qkv_rope: head size %d must be a multiple of 16", d);
     FD_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
                (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 && (uintptr_t)cos_t % 16 == 0 &&
-               (uintptr_t)sin_t % 16 == 0, -2, "gemm_tc_qkv_rope: all arrays must be 16-byte aligned");
+               (uintptr_t)sin_t % 16 == 0 && (uintptr_t)bias % 16 == 0, -2, "gemm_tc_qkv_rope: all arrays must be 16-byte aligned");
     TcParams p;
     p.bias = bias; p.out = q_out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = 4; p.bias_f32 = bias_f32;
     TcRope ra;
