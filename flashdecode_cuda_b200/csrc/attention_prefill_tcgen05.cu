@@ -36,7 +36,8 @@ constexpr int TA_D = 128;                 // head size
 constexpr int TA_BM = 128;                // queries per CTA
 constexpr int TA_BN = 64;                 // keys per tile
 constexpr int TA_STAGES = 4;              // key/value tiles in flight
-constexpr int TA_THREADS = 192;
+constexpr int TA_PV_WARP = 6;              // warps: 0 TMA, 1 issuer of Q K^T, 2-5 softmax, 6 issuer of P V
+constexpr int TA_THREADS = 224;
 constexpr int TA_QSLAB = TA_BM * 128;     // bytes of a [128 queries][64 bf16] slab (Q: two of them; P: one)
 constexpr int TA_KSLAB = TA_BN * 128;     // bytes of a [64 keys][64 bf16] slab (K and V: two each)
 constexpr int TA_QTILE = 2 * TA_QSLAB;    // Q [128][128]
@@ -44,7 +45,7 @@ constexpr int TA_PTILE = TA_QSLAB;        // P [128][64]
 constexpr int TA_KTILE = 2 * TA_KSLAB;    // K or V [64][128]
 // 176 KB + barriers, one CTA per SM: four key/value tiles in flight hide the copies' latency (measured:
 // better than two CTAs per SM with two tiles each, 54 against 69 us for a 2,048-token prompt)
-constexpr int TA_SMEM = TA_QTILE + TA_PTILE + TA_STAGES * 2 * TA_KTILE + 128;
+constexpr int TA_SMEM = TA_QTILE + TA_PTILE + TA_STAGES * 2 * TA_KTILE + 256;
 constexpr unsigned long long TA_WAIT_NS = 200ull * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t ta_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -143,11 +144,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* p_s = q_s + TA_QTILE;                     // [128 q][64 keys]
     unsigned char* kv_s = p_s + TA_PTILE;                    // per stage: K [2 slabs][64 keys][64 d], V the same
     uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + TA_STAGES * 2 * TA_KTILE);
-    // bars: [0] q_full, kv_full[S], kv_empty[S], s_full[2], p_ready, o_done
+    // bars: [0] q_full, kv_full[S], kv_empty[S], s_full[2], s_free[2], p_ready, o_done
     uint64_t* kv_full = bars + 1;
     uint64_t* kv_empty = kv_full + TA_STAGES;
     uint64_t* s_full = kv_empty + TA_STAGES;
-    uint64_t* p_ready = s_full + 2;
+    uint64_t* s_free = s_full + 2;
+    uint64_t* p_ready = s_free + 2;
     uint64_t* o_done = p_ready + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -183,6 +185,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&s_full[0])) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&s_full[1])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(ta_saddr(&s_free[0])) : "memory");   // every softmax thread arrives
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(ta_saddr(&s_free[1])) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(ta_saddr(p_ready)) : "memory");   // every softmax thread arrives
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(o_done)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -252,15 +256,19 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int it = max(0, issued - TA_STAGES); it < issued; ++it)
                 ta_wait(ta_saddr(&kv_full[it % TA_STAGES]), (it / TA_STAGES) & 1, abort_flag + 1, nullptr);
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ----
-        // D float, A and B bf16, M 128.  QK^T: N = 64 keys, both K-major; PV: N = 128 dims, B (= V) MN-major
+        // ---- issuer of S = Q K^T ----
+        // D float, A and B bf16, M 128, N = 64 keys, both operands K-major.  S(it) goes into the S tile it & 1 as
+        // soon as the softmax warps have taken S(it - 2) out of it (s_free) - long before they are done with it -
+        // so the scores of the next tile are always ready; P V has an issuer of its own (below), because one
+        // thread issuing both took 0.6 us per tile, on the critical path between two softmax steps.
         const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TA_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        const uint32_t qa = ta_saddr(q_s), pa = ta_saddr(p_s);
-        // S(it) = Q K(it)^T into the S tile it & 1; the barrier s_full[it & 1] completes with it
-        auto issue_qk = [&](int it) -> bool {
+        const uint32_t qa = ta_saddr(q_s);
+        bool ok = ta_wait(ta_saddr(&bars[0]), 0, abort_flag, p.status);
+        for (int it = 0; ok && it < n_tiles; ++it) {
             const int s = it % TA_STAGES;
-            if (!ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status)) return false;
+            ok = ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status);
+            if (ok && it >= 2) ok = ta_wait(ta_saddr(&s_free[it & 1]), ((it >> 1) - 1) & 1, abort_flag, p.status);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t ks = ta_saddr(kv_s + s * 2 * TA_KTILE);
 #pragma unroll
@@ -270,28 +278,33 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                        ta_desc_k(ks + (kk >> 2) * TA_KSLAB + inner), idesc_qk, kk != 0);
             }
             ta_commit(ta_saddr(&s_full[it & 1]));
-            return true;
-        };
-        bool ok = ta_wait(ta_saddr(&bars[0]), 0, abort_flag, p.status);
-        if (ok) ok = issue_qk(0);
-        for (int it = 0; ok && it < n_tiles; ++it) {
-            // the next tile's scores are under way while the softmax warps work on this one: its S tile
-            // was read to the end before p_ready(it - 1), which the last iteration waited for
-            if (it + 1 < n_tiles) { ok = issue_qk(it + 1); if (!ok) break; }
-            ok = ta_wait(ta_saddr(p_ready), it & 1, abort_flag, p.status);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int s = it % TA_STAGES;
-            const uint32_t vs = ta_saddr(kv_s + s * 2 * TA_KTILE + TA_KTILE);
-#pragma unroll
-            for (int kk = 0; kk < TA_BN / 16; ++kk)            // 4 steps over the keys
-                ta_mma(tmem_o, ta_desc_k(pa + kk * 32), ta_desc_mn(vs + kk * 2048, TA_KSLAB), idesc_pv, (it | kk) != 0);
-            ta_commit(ta_saddr(&kv_empty[s]));
-            ta_commit(ta_saddr(o_done));
         }
-        if (!ok) { ta_commit(ta_saddr(&s_full[0])); ta_commit(ta_saddr(&s_full[1])); ta_commit(ta_saddr(o_done)); }
-    } else if (warp >= 2) {
-        // ---- softmax and epilogue: thread = query row ----
+        if (!ok) { ta_commit(ta_saddr(&s_full[0])); ta_commit(ta_saddr(&s_full[1])); }
+    } else if (warp == TA_PV_WARP) {
+        if (lane == 0) {
+            // ---- issuer of O += P V: N = 128 dims, B (= V) MN-major ----
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TA_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            const uint32_t pa = ta_saddr(p_s);
+            bool ok = true;
+            for (int it = 0; ok && it < n_tiles; ++it) {
+                const int s = it % TA_STAGES;
+                // the tile's copies have landed (the other issuer saw it long ago; this thread must see it too)
+                ok = ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status);
+                if (ok) ok = ta_wait(ta_saddr(p_ready), it & 1, abort_flag, p.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t vs = ta_saddr(kv_s + s * 2 * TA_KTILE + TA_KTILE);
+#pragma unroll
+                for (int kk = 0; kk < TA_BN / 16; ++kk)        // 4 steps over the keys
+                    ta_mma(tmem_o, ta_desc_k(pa + kk * 32), ta_desc_mn(vs + kk * 2048, TA_KSLAB), idesc_pv, (it | kk) != 0);
+                // Q K^T of this tile completed before its scores were read, so both products are done with the stage
+                ta_commit(ta_saddr(&kv_empty[s]));
+                ta_commit(ta_saddr(o_done));
+            }
+            if (!ok) ta_commit(ta_saddr(o_done));
+        }
+    } else if (warp >= 2 && warp < 6) {
+        // ---- softmax and epilogue (warps 2-5): thread = query row ----
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -311,6 +324,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ta_ld32(tmem_s + (it & 1) * TA_BN + lane_base + 32, v + 32);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             }
+            // the scores are in registers: the S tile may take the tile after next
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            ta_arrive(ta_saddr(&s_free[it & 1]));
             const bool need_mask = t0 + TA_BN - 1 > p_first || t0 < lo || t0 + TA_BN > hi ||
                                    (p.window > 0 && t0 < p_first + TA_BM - p.window);
             if (need_mask) {
