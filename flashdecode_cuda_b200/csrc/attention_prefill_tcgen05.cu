@@ -1,25 +1,34 @@
 // Prompt attention on the 5th-generation tensor cores (head size 128, bfloat16):
 // causal, grouped-query, paged, variable lengths, optional window, continuing a
-// cached prefix.  A CTA takes 128 consecutive query tokens of one sequence and
-// one query head and walks the keys in tiles of 64:
+// cached prefix.  A CTA takes 256 consecutive query tokens of one sequence and
+// one query head as two query tiles of 128 rows, and walks the keys in tiles of
+// 64 that both query tiles share (each is fetched once):
 //
 //   S[128 q, 64 keys] = Q K^T      tcgen05.mma, both operands K-major in shared memory,
-//                                  accumulator S in tensor memory (two tiles of 64 columns: the
-//                                  next tile's scores are computed while the softmax works)
-//   softmax                        4 warps, one thread per query row: tcgen05.ld of its S row,
-//                                  running max / sum in float (base 2), P written to shared
-//                                  memory as bfloat16 in the 128-byte-swizzled K-major layout
+//                                  accumulator S in tensor memory (per query tile two buffers
+//                                  of 64 columns: the next scores are computed while the
+//                                  softmax works on these)
+//   softmax                        4 warps per query tile, one thread per query row:
+//                                  tcgen05.ld of its S row, running max / sum in float (base
+//                                  2), P written to shared memory as bfloat16 in the
+//                                  128-byte-swizzled K-major layout
 //   O[128 q, 128 d] += P V         tcgen05.mma with V as an MN-major operand (V rows are keys,
 //                                  the head dimension is contiguous), accumulator O in tensor
-//                                  memory (128 more columns), rescaled in place when a row's
-//                                  maximum grew by more than 2^8
+//                                  memory (128 columns per query tile), rescaled in place when
+//                                  a row's maximum grew by more than 2^8
+//
+// The two query tiles run the same steps out of phase: while one's softmax warps
+// are in their exp phase (bound by the special-function units), the other's are
+// waiting, packing or storing, and the tensor cores serve both.  All 512 columns
+// of tensor memory are in use (2 x 2 x 64 for S, 2 x 128 for O).
 //
 // Keys and values come straight from the paged pools by TMA: one 2-D box of
 // (block_size keys x 64 dims) per cache block and half head, placed so that a
-// tile of 64 keys forms the canonical swizzled layout; four tiles are in
+// tile of 64 keys forms the canonical swizzled layout; three tiles are in
 // flight.  Roles: warp 0 issues TMA (the copies of a tile from as many lanes at
-// once, the block numbers fetched 32 at a time ahead of use), warp 1 issues MMAs
-// and owns the tensor-memory allocation, warps 2-5 do the softmax and the epilogue.  Every mbarrier wait is bounded in time; a wait
+// once, the block numbers fetched 32 at a time ahead of use), warp 1 issues
+// Q K^T and owns the tensor-memory allocation, warps 2-9 do the softmax and the
+// epilogue, warp 10 issues P V.  Every mbarrier wait is bounded in time; a wait
 // that runs out sets a status bit and the CTA winds down (see gemm_tcgen05.cu).
 #include <cuda.h>
 #include <math.h>
@@ -33,19 +42,21 @@
 namespace fd {
 
 constexpr int TA_D = 128;                 // head size
-constexpr int TA_BM = 128;                // queries per CTA
+constexpr int TA_BM = 128;                // queries per query tile (the M of the MMAs)
 constexpr int TA_BN = 64;                 // keys per tile
-constexpr int TA_STAGES = 4;              // key/value tiles in flight
-constexpr int TA_PV_WARP = 6;              // warps: 0 TMA, 1 issuer of Q K^T, 2-5 softmax, 6 issuer of P V
-constexpr int TA_THREADS = 224;
+constexpr int TA_STAGES = 3;              // key/value tiles in flight
+constexpr int TA_NQ = 2;                  // query tiles per CTA
+constexpr int TA_ROWS = TA_NQ * TA_BM;    // queries per CTA
+constexpr int TA_PV_WARP = 2 + 4 * TA_NQ;  // warps: 0 TMA, 1 issuer of Q K^T, 2-9 softmax (four per query tile), 10 issuer of P V
+constexpr int TA_THREADS = (TA_PV_WARP + 1) * 32;
 constexpr int TA_QSLAB = TA_BM * 128;     // bytes of a [128 queries][64 bf16] slab (Q: two of them; P: one)
 constexpr int TA_KSLAB = TA_BN * 128;     // bytes of a [64 keys][64 bf16] slab (K and V: two each)
 constexpr int TA_QTILE = 2 * TA_QSLAB;    // Q [128][128]
 constexpr int TA_PTILE = TA_QSLAB;        // P [128][64]
 constexpr int TA_KTILE = 2 * TA_KSLAB;    // K or V [64][128]
-// 176 KB + barriers, one CTA per SM: four key/value tiles in flight hide the copies' latency (measured:
-// better than two CTAs per SM with two tiles each, 54 against 69 us for a 2,048-token prompt)
-constexpr int TA_SMEM = TA_QTILE + TA_PTILE + TA_STAGES * 2 * TA_KTILE + 256;
+// 192 KB + barriers, one CTA per SM: two query tiles (Q 32 KB and P 16 KB each) and three key/value tiles
+// in flight (32 KB each)
+constexpr int TA_SMEM = TA_NQ * (TA_QTILE + TA_PTILE) + TA_STAGES * 2 * TA_KTILE + 256;
 constexpr unsigned long long TA_WAIT_NS = 200ull * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t ta_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -140,18 +151,18 @@ __global__ void __launch_bounds__(TA_THREADS, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ __align__(1024) unsigned char ta_raw[];
-    unsigned char* q_s = ta_raw;                             // [2 slabs][128 q][64 d]
-    unsigned char* p_s = q_s + TA_QTILE;                     // [128 q][64 keys]
-    unsigned char* kv_s = p_s + TA_PTILE;                    // per stage: K [2 slabs][64 keys][64 d], V the same
+    unsigned char* q_s = ta_raw;                             // per query tile: [2 slabs][128 q][64 d]
+    unsigned char* p_s = q_s + TA_NQ * TA_QTILE;             // per query tile: [128 q][64 keys]
+    unsigned char* kv_s = p_s + TA_NQ * TA_PTILE;            // per stage: K [2 slabs][64 keys][64 d], V the same
     uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + TA_STAGES * 2 * TA_KTILE);
-    // bars: [0] q_full, kv_full[S], kv_empty[S], s_full[2], s_free[2], p_ready, o_done
+    // bars: [0] q_full, kv_full[S], kv_empty[S]; per query tile: s_full[2], s_free[2], p_ready, o_done
     uint64_t* kv_full = bars + 1;
     uint64_t* kv_empty = kv_full + TA_STAGES;
-    uint64_t* s_full = kv_empty + TA_STAGES;
-    uint64_t* s_free = s_full + 2;
-    uint64_t* p_ready = s_free + 2;
-    uint64_t* o_done = p_ready + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+    uint64_t* s_full = kv_empty + TA_STAGES;                 // [qt][2]
+    uint64_t* s_free = s_full + 2 * TA_NQ;                   // [qt][2]
+    uint64_t* p_ready = s_free + 2 * TA_NQ;                  // [qt]
+    uint64_t* o_done = p_ready + TA_NQ;                      // [qt]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + TA_NQ);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -159,55 +170,70 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int slot = p.row_slot[b];
     const int q_len = slot >= 0 ? p.row_q_len[b] : 0;
-    if (tile * TA_BM >= q_len) return;                       // uniform for the CTA; nothing allocated yet
+    if (tile * TA_ROWS >= q_len) return;                     // uniform for the CTA; nothing allocated yet
     if ((ta_saddr(ta_raw) & 1023u) != 0) {                   // the swizzled tiles need a 1024-byte-aligned base
         if (threadIdx.x == 0) set_status(p.status, STATUS_WAIT_TIMEOUT);
         return;
     }
     const int ctx = p.row_ctx_len[b];
-    const int tok0 = p.row_q_start[b] + tile * TA_BM;
-    const int nq = min(TA_BM, q_len - tile * TA_BM);
+    const int tok0 = p.row_q_start[b] + tile * TA_ROWS;      // first token of the CTA
     const int kvh = h / p.G;
-    const int p_first = ctx + tile * TA_BM;
-    const int hi = p_first + nq;
-    const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
     const int bs = p.block_size;
+    // The CTA's two query tiles (128 rows each; the second may be empty) share every key tile.  Of the key
+    // tiles t_begin + 64 it, it = 0 .. n_tiles - 1, query tile qt takes it_lo[qt] .. it_hi[qt] - 1: causality
+    // ends the first tile's range two key tiles early, a window starts the second's two key tiles late.
+    int nq[TA_NQ], p_first[TA_NQ], q_lo[TA_NQ], q_hi[TA_NQ], it_lo[TA_NQ], it_hi[TA_NQ];
+#pragma unroll
+    for (int qt = 0; qt < TA_NQ; ++qt) {
+        nq[qt] = max(0, min(TA_BM, q_len - tile * TA_ROWS - qt * TA_BM));
+        p_first[qt] = ctx + tile * TA_ROWS + qt * TA_BM;
+        q_hi[qt] = p_first[qt] + nq[qt];
+        q_lo[qt] = p.window > 0 ? max(0, p_first[qt] - p.window + 1) : 0;
+    }
+    const int lo = q_lo[0];
+    const int hi = nq[1] > 0 ? q_hi[1] : q_hi[0];
     const int t_begin = (lo / TA_BN) * TA_BN;
     const int n_tiles = (hi - t_begin + TA_BN - 1) / TA_BN;
+#pragma unroll
+    for (int qt = 0; qt < TA_NQ; ++qt) {
+        it_lo[qt] = (q_lo[qt] / TA_BN * TA_BN - t_begin) / TA_BN;
+        it_hi[qt] = nq[qt] > 0 ? (q_hi[qt] - t_begin + TA_BN - 1) / TA_BN : it_lo[qt];
+    }
 
     if (threadIdx.x == 0) {
         abort_flag[0] = 0;
         abort_flag[1] = 0;
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&bars[0])) : "memory");
-        for (int s = 0; s < TA_STAGES; ++s) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&kv_full[s])) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&kv_empty[s])) : "memory");
-        }
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&s_full[0])) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(&s_full[1])) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(ta_saddr(&s_free[0])) : "memory");   // every softmax thread arrives
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(ta_saddr(&s_free[1])) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(ta_saddr(p_ready)) : "memory");   // every softmax thread arrives
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(ta_saddr(o_done)) : "memory");
+        auto init = [](uint64_t* bar, int count) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ta_saddr(bar)), "r"(count) : "memory");
+        };
+        init(&bars[0], 1);
+        for (int s = 0; s < TA_STAGES; ++s) { init(&kv_full[s], 1); init(&kv_empty[s], 1); }
+        for (int i = 0; i < 2 * TA_NQ; ++i) { init(&s_full[i], 1); init(&s_free[i], 128); }   // s_free, p_ready: every softmax thread arrives
+        for (int qt = 0; qt < TA_NQ; ++qt) { init(&p_ready[qt], 128); init(&o_done[qt], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ta_saddr(tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ta_saddr(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 128;       // columns 0..63 and 64..127: two S tiles, 128..255: O
+    // columns: S of query tile qt, buffer j at 128 qt + 64 j; O of query tile qt at 256 + 128 qt
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 256;
 
     if (warp == 0) {
         // ---- TMA producer: the warp's lanes fetch the block numbers of the
         // next 32 copies together, one chunk ahead, so that no copy waits for a table entry ----
         if (lane == 0) {
-            ta_expect(ta_saddr(&bars[0]), TA_QTILE);
-            ta_tma(ta_saddr(q_s), &map_q, ta_saddr(&bars[0]), h * TA_D, tok0);
-            ta_tma(ta_saddr(q_s + TA_QSLAB), &map_q, ta_saddr(&bars[0]), h * TA_D + 64, tok0);
+            // rows beyond the last token of the step are zero-filled; rows of a following sequence are computed and dropped
+            ta_expect(ta_saddr(&bars[0]), TA_NQ * TA_QTILE);
+#pragma unroll
+            for (int qt = 0; qt < TA_NQ; ++qt) {
+                ta_tma(ta_saddr(q_s + qt * TA_QTILE), &map_q, ta_saddr(&bars[0]), h * TA_D, tok0 + qt * TA_BM);
+                ta_tma(ta_saddr(q_s + qt * TA_QTILE + TA_QSLAB), &map_q, ta_saddr(&bars[0]), h * TA_D + 64, tok0 + qt * TA_BM);
+            }
         }
         const int first_col = lo / bs;                        // blocks behind a window may have been given back
         const int last_col = (hi - 1) / bs;                   // last block column that holds a key of this CTA
@@ -257,88 +283,105 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ta_wait(ta_saddr(&kv_full[it % TA_STAGES]), (it / TA_STAGES) & 1, abort_flag + 1, nullptr);
     } else if (warp == 1 && lane == 0) {
         // ---- issuer of S = Q K^T ----
-        // D float, A and B bf16, M 128, N = 64 keys, both operands K-major.  S(it) goes into the S tile it & 1 as
-        // soon as the softmax warps have taken S(it - 2) out of it (s_free) - long before they are done with it -
-        // so the scores of the next tile are always ready; P V has an issuer of its own (below), because one
-        // thread issuing both took 0.6 us per tile, on the critical path between two softmax steps.
+        // D float, A and B bf16, M 128, N = 64 keys, both operands K-major.  S of a query tile's j-th key tile
+        // goes into its S buffer j & 1 as soon as the softmax warps have taken the scores before last out of it
+        // (s_free) - long before they are done with them - so the next scores are always ready; P V has an
+        // issuer of its own (below): one thread issuing both took 0.6 us per tile, between two softmax steps.
         const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        const uint32_t qa = ta_saddr(q_s);
         bool ok = ta_wait(ta_saddr(&bars[0]), 0, abort_flag, p.status);
         for (int it = 0; ok && it < n_tiles; ++it) {
             const int s = it % TA_STAGES;
             ok = ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status);
-            if (ok && it >= 2) ok = ta_wait(ta_saddr(&s_free[it & 1]), ((it >> 1) - 1) & 1, abort_flag, p.status);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t ks = ta_saddr(kv_s + s * 2 * TA_KTILE);
 #pragma unroll
-            for (int kk = 0; kk < TA_D / 16; ++kk) {           // 8 steps over the head dimension
-                const uint32_t inner = (kk & 3) * 32;
-                ta_mma(tmem_s + (it & 1) * TA_BN, ta_desc_k(qa + (kk >> 2) * TA_QSLAB + inner),
-                       ta_desc_k(ks + (kk >> 2) * TA_KSLAB + inner), idesc_qk, kk != 0);
+            for (int qt = 0; qt < TA_NQ; ++qt) {
+                if (!ok || it < it_lo[qt] || it >= it_hi[qt]) continue;
+                const int j = it - it_lo[qt];
+                if (j >= 2) ok = ta_wait(ta_saddr(&s_free[qt * 2 + (j & 1)]), ((j >> 1) - 1) & 1, abort_flag, p.status);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t qa = ta_saddr(q_s + qt * TA_QTILE);
+#pragma unroll
+                for (int kk = 0; kk < TA_D / 16; ++kk) {       // 8 steps over the head dimension
+                    const uint32_t inner = (kk & 3) * 32;
+                    ta_mma(tmem_s + qt * 128 + (j & 1) * TA_BN, ta_desc_k(qa + (kk >> 2) * TA_QSLAB + inner),
+                           ta_desc_k(ks + (kk >> 2) * TA_KSLAB + inner), idesc_qk, kk != 0);
+                }
+                ta_commit(ta_saddr(&s_full[qt * 2 + (j & 1)]));
             }
-            ta_commit(ta_saddr(&s_full[it & 1]));
         }
-        if (!ok) { ta_commit(ta_saddr(&s_full[0])); ta_commit(ta_saddr(&s_full[1])); }
+        if (!ok) for (int i = 0; i < 2 * TA_NQ; ++i) ta_commit(ta_saddr(&s_full[i]));
     } else if (warp == TA_PV_WARP) {
         if (lane == 0) {
             // ---- issuer of O += P V: N = 128 dims, B (= V) MN-major ----
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TA_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-            const uint32_t pa = ta_saddr(p_s);
             bool ok = true;
             for (int it = 0; ok && it < n_tiles; ++it) {
                 const int s = it % TA_STAGES;
                 // the tile's copies have landed (the other issuer saw it long ago; this thread must see it too)
                 ok = ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status);
-                if (ok) ok = ta_wait(ta_saddr(p_ready), it & 1, abort_flag, p.status);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t vs = ta_saddr(kv_s + s * 2 * TA_KTILE + TA_KTILE);
 #pragma unroll
-                for (int kk = 0; kk < TA_BN / 16; ++kk)        // 4 steps over the keys
-                    ta_mma(tmem_o, ta_desc_k(pa + kk * 32), ta_desc_mn(vs + kk * 2048, TA_KSLAB), idesc_pv, (it | kk) != 0);
-                // Q K^T of this tile completed before its scores were read, so both products are done with the stage
-                ta_commit(ta_saddr(&kv_empty[s]));
-                ta_commit(ta_saddr(o_done));
+                for (int qt = 0; qt < TA_NQ; ++qt) {
+                    if (!ok || it < it_lo[qt] || it >= it_hi[qt]) continue;
+                    const int j = it - it_lo[qt];
+                    ok = ta_wait(ta_saddr(&p_ready[qt]), j & 1, abort_flag, p.status);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t pa = ta_saddr(p_s + qt * TA_PTILE);
+#pragma unroll
+                    for (int kk = 0; kk < TA_BN / 16; ++kk)    // 4 steps over the keys
+                        ta_mma(tmem_o + qt * TA_D, ta_desc_k(pa + kk * 32), ta_desc_mn(vs + kk * 2048, TA_KSLAB), idesc_pv,
+                               (j | kk) != 0);
+                    ta_commit(ta_saddr(&o_done[qt]));
+                }
+                // Q K^T of this key tile completed before its scores were read, so every product is done with the stage
+                if (ok) ta_commit(ta_saddr(&kv_empty[s]));
             }
-            if (!ok) ta_commit(ta_saddr(o_done));
+            if (!ok) for (int qt = 0; qt < TA_NQ; ++qt) ta_commit(ta_saddr(&o_done[qt]));
         }
-    } else if (warp >= 2 && warp < 6) {
-        // ---- softmax and epilogue (warps 2-5): thread = query row ----
-        const int quarter = warp & 3;
+    } else if (warp >= 2 && warp < 2 + 4 * TA_NQ) {
+        // ---- softmax and epilogue (warps 2-5: first query tile, 6-9: second): thread = query row ----
+        const int qt = (warp - 2) >> 2;
+        const int quarter = warp & 3;                               // the quarter of the tensor-memory lanes this warp may touch
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const int pos = p_first + r;
+        const int pos = p_first[qt] + r;
+        const int my_lo = q_lo[qt], my_hi = q_hi[qt];
         const float scale_log2 = p.scale * 1.4426950408889634f;   // > 0: the maximum is taken over raw scores
         float m_run = -INFINITY, l_run = 0.f;                      // running maximum (raw score) and sum
         bool ok = true;
-        for (int it = 0; it < n_tiles; ++it) {
+        const int n_mine = it_hi[qt] - it_lo[qt];
+        unsigned char* my_p = p_s + qt * TA_PTILE;
+        const uint32_t my_o = tmem_o + qt * TA_D;
+        for (int j = 0; j < n_mine; ++j) {
+            const int it = it_lo[qt] + j;
             const int t0 = t_begin + it * TA_BN;
-            ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&s_full[it & 1]), (it >> 1) & 1, abort_flag, p.status));
+            ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&s_full[qt * 2 + (j & 1)]), (j >> 1) & 1, abort_flag, p.status));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float x[TA_BN];
             {
                 uint32_t* v = reinterpret_cast<uint32_t*>(x);
-                ta_ld32(tmem_s + (it & 1) * TA_BN + lane_base, v);
-                ta_ld32(tmem_s + (it & 1) * TA_BN + lane_base + 32, v + 32);
+                ta_ld32(tmem_s + qt * 128 + (j & 1) * TA_BN + lane_base, v);
+                ta_ld32(tmem_s + qt * 128 + (j & 1) * TA_BN + lane_base + 32, v + 32);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             }
-            // the scores are in registers: the S tile may take the tile after next
+            // the scores are in registers: the S buffer may take the key tile after next
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            ta_arrive(ta_saddr(&s_free[it & 1]));
-            const bool need_mask = t0 + TA_BN - 1 > p_first || t0 < lo || t0 + TA_BN > hi ||
-                                   (p.window > 0 && t0 < p_first + TA_BM - p.window);
+            ta_arrive(ta_saddr(&s_free[qt * 2 + (j & 1)]));
+            const bool need_mask = t0 + TA_BN - 1 > p_first[qt] || t0 < my_lo || t0 + TA_BN > my_hi ||
+                                   (p.window > 0 && t0 < p_first[qt] + TA_BM - p.window);
             if (need_mask) {
 #pragma unroll
-                for (int j = 0; j < TA_BN; ++j) {
-                    const int t = t0 + j;
-                    if (!(t >= lo && t < hi && t <= pos && (p.window <= 0 || pos - t < p.window))) x[j] = -INFINITY;
+                for (int c = 0; c < TA_BN; ++c) {
+                    const int t = t0 + c;
+                    if (!(t >= my_lo && t < my_hi && t <= pos && (p.window <= 0 || pos - t < p.window))) x[c] = -INFINITY;
                 }
             }
             float mx4[4] = {x[0], x[1], x[2], x[3]};          // four chains instead of one of 63 dependent steps
 #pragma unroll
-            for (int j = 4; j < TA_BN; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], x[j]);
+            for (int c = 4; c < TA_BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], x[c]);
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // The maximum moves only when it grows by more than 2^8 (P stays below 256, exact enough in
             // bfloat16 and far from overflow in the 32-bit sums): most tiles then need no rescaling of O
@@ -350,42 +393,43 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             float rs4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t packed[TA_BN / 2];
 #pragma unroll
-            for (int j = 0; j < TA_BN; j += 2) {
-                const float p0 = ta_ex2(fmaf(x[j], scale_log2, -m_off));
-                const float p1 = ta_ex2(fmaf(x[j + 1], scale_log2, -m_off));
-                rs4[(j >> 1) & 3] += p0 + p1;
+            for (int c = 0; c < TA_BN; c += 2) {
+                const float p0 = ta_ex2(fmaf(x[c], scale_log2, -m_off));
+                const float p1 = ta_ex2(fmaf(x[c + 1], scale_log2, -m_off));
+                rs4[(c >> 1) & 3] += p0 + p1;
                 const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-                packed[j >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+                packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
             }
             l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
             // The previous P V must be complete before P is overwritten and before O is touched;
             // then O *= alpha where a maximum moved
-            if (it > 0) {
-                ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(o_done), (it - 1) & 1, abort_flag, p.status));
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (j - 1) & 1, abort_flag, p.status));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
                     for (int c0 = 0; c0 < TA_D; c0 += 32) {
                         uint32_t v[32];
-                        ta_ld32(tmem_o + lane_base + c0, v);
+                        ta_ld32(my_o + lane_base + c0, v);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-                        ta_st32(tmem_o + lane_base + c0, v);
+                        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
+                        ta_st32(my_o + lane_base + c0, v);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
             }
             // P as bfloat16 into shared memory: K-major rows of 128 bytes, 16-byte chunks swizzled by the row
-            unsigned char* prow = p_s + r * 128;
+            unsigned char* prow = my_p + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) =
                     make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
-            // Rows of V that belong to no key of this request (the unused tail of its last cache block, a
-            // block that stands in for one outside its range) may hold anything, even NaN, and 0 * NaN is
-            // NaN: zero them.  The tile has landed (S was computed from it).
+            // Rows of V that belong to no key of this CTA's range (the unused tail of the last cache block, a
+            // block that stands in for one outside the range) may hold anything, even NaN, and 0 * NaN is NaN:
+            // zero them.  The tile has landed (S was computed from it).  Both query tiles do it (the same zeros),
+            // each before its own P V is allowed to start.
             if (r < TA_BN && (t0 + r < lo || t0 + r >= hi)) {
                 unsigned char* vrow = kv_s + (it % TA_STAGES) * 2 * TA_KTILE + TA_KTILE + r * 128;
 #pragma unroll
@@ -397,29 +441,29 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // P and V (generic-proxy stores) must be visible to the tensor core's reads of shared memory
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            ta_arrive(ta_saddr(p_ready));
+            ta_arrive(ta_saddr(&p_ready[qt]));
         }
-        if (ok) ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(o_done), (n_tiles - 1) & 1, abort_flag, p.status));
+        if (ok && n_mine > 0) ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (n_mine - 1) & 1, abort_flag, p.status));
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        if (ok && n_mine > 0) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + ((size_t)(tok0 + r) * p.n_q + h) * TA_D;
+            __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + ((size_t)(tok0 + qt * TA_BM + r) * p.n_q + h) * TA_D;
 #pragma unroll 1
             for (int c0 = 0; c0 < TA_D; c0 += 32) {
                 uint32_t v[32];
-                ta_ld32(tmem_o + lane_base + c0, v);
+                ta_ld32(my_o + lane_base + c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (r < nq) {
+                if (r < nq[qt]) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
+                    for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(v[j + 2 * e]) * inv,
-                                                                            __uint_as_float(v[j + 2 * e + 1]) * inv);
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * e]) * inv,
+                                                                            __uint_as_float(v[c + 2 * e + 1]) * inv);
                             w[e] = *reinterpret_cast<const uint32_t*>(&pk);
                         }
-                        *reinterpret_cast<uint4*>(orow + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(orow + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
@@ -429,7 +473,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
 }
 
@@ -496,7 +540,7 @@ int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_
         if (e != cudaSuccess) return fail(-3, "attention: cannot get %d bytes of shared memory: %s", TA_SMEM, cudaGetErrorString(e));
         configured = true;
     }
-    const int q_tiles = (max_q_len + TA_BM - 1) / TA_BM;
+    const int q_tiles = (max_q_len + TA_ROWS - 1) / TA_ROWS;
     dim3 grid(q_tiles, p.n_q, n_rows);
     attn_prefill_tcgen05_kernel<<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p);
     return check_launch("attention_prefill_tcgen05");
