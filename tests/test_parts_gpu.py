@@ -1,7 +1,9 @@
-"""Each part alone against the plain function of the same name, and a toy
-architecture defined here - a mixer with fixed-size state of its own, mixed
-with attention layers, one layer run twice, one entry reading another's cache -
-registered, built and stepped without touching the framework's files."""
+"""Each part alone against the plain function of the same name, and two toy
+architectures defined here - a mixer with fixed-size state of its own, mixed
+with attention layers, one layer run twice, one entry reading another's cache;
+a feed-forward with routing, a position encoding that is not rotary, layers
+that differ in mixer and in feed-forward - registered, built and stepped
+without touching the framework's files."""
 
 import json
 import math
@@ -270,4 +272,178 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
     # and through the generation loop (eager steps, since the toy mixer decides on the host)
     res = eng.generate(prompts[:2], 5)
     assert all(len(r.tokens) == 5 for r in res)
+    model.check_status()
+
+
+# ---------------------------------------------------------------------------
+# a second toy architecture: another position encoding and a feed-forward with routing
+# ---------------------------------------------------------------------------
+
+@fd.register_part("position", "toy_sinusoid_table")
+class SinusoidTable(fd.parts.Position):
+    """table[p, i] = 1 + amp * sin(p / period + i): multiplied into the activations by the mixer below.
+    No weights; built for as many positions as the cache holds."""
+
+    def __init__(self, size, period, amp, max_positions):
+        self.size, self.period, self.amp, self.max_positions = size, float(period), float(amp), max_positions
+        self.table = None
+
+    def prepare(self, n_positions, rt):
+        n = min(n_positions, self.max_positions)
+        if self.table is None or self.table.shape[0] < n:
+            p = torch.arange(n, dtype=torch.float32)[:, None]
+            i = torch.arange(self.size, dtype=torch.float32)[None, :]
+            self.table = (1.0 + self.amp * torch.sin(p / self.period + i)).to(rt.device)
+
+
+@fd.register_part("mixer", "toy_position_gate")
+class PositionGate(Mixer):
+    """delta_t = W (x_t * table[pos_t]): no cache at all, the position comes from the step's index arrays."""
+
+    def __init__(self, prefix, hidden_size, position):
+        self.prefix, self.H, self.position = prefix, hidden_size, position
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.gate.weight", (self.H, self.H))]
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.w = tensors[f"{self.prefix}.gate.weight"]
+
+    def forward(self, ctx, x, lc: LayerCache):
+        gate = self.position.table[ctx.tok_pos.long()]
+        return ((x.float() * gate) @ self.w.float().T).to(x.dtype)
+
+
+@fd.register_part("feed_forward", "toy_top1_experts")
+class Top1Experts(fd.parts.FeedForward):
+    """Router logits in float32, the best expert alone (lowest index wins ties), one matrix per expert."""
+
+    def __init__(self, prefix, hidden_size, n_experts):
+        self.prefix, self.H, self.E = prefix, hidden_size, n_experts
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.router.weight", (self.E, self.H), "vector"),      # stays 32-bit if stored so
+                TensorSpec(f"{self.prefix}.experts.weight", (self.E * self.H, self.H))]
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.router = tensors[f"{self.prefix}.router.weight"]
+        self.experts = tensors[f"{self.prefix}.experts.weight"].view(self.E, self.H, self.H)
+
+    def forward(self, ctx, x):
+        choice = (x.float() @ self.router.float().T).argmax(-1)
+        return torch.bmm(self.experts[choice].float(), x.float()[:, :, None])[:, :, 0].to(x.dtype)
+
+
+@dataclass
+class Toy2Config:
+    hidden_size: int
+    vocab_size: int
+    n_experts: int
+    eps: float
+    architecture: str = "Toy2ForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["hidden_size"], d["vocab_size"], d["n_experts"], d["eps"])
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                "n_experts": self.n_experts, "eps": self.eps}
+
+
+def toy2_blueprint(cfg: Toy2Config) -> ModelBlueprint:
+    H = cfg.hidden_size
+    norm = lambda name: PartSpec("norm", "rmsnorm", dict(size=H, eps=cfg.eps), name)
+
+    def layer(i, mixer, ff):
+        return LayerSpec("prenorm", norm(f"t2.layers.{i}.n1"), mixer, norm(f"t2.layers.{i}.n2"), ff)
+    gate = lambda i: PartSpec("mixer", "toy_position_gate", dict(hidden_size=H, position="sinus"), f"t2.layers.{i}")
+    attn = lambda i: PartSpec("mixer", "gqa_attention", dict(hidden_size=H, n_heads=2, n_kv_heads=2, head_dim=16,
+                                                            position="rope", bias=False), f"t2.layers.{i}.attn")
+    routed = lambda i: PartSpec("feed_forward", "toy_top1_experts", dict(hidden_size=H, n_experts=cfg.n_experts),
+                                f"t2.layers.{i}.moe")
+    dense = lambda i: PartSpec("feed_forward", "swiglu", dict(hidden_size=H, intermediate_size=2 * H), f"t2.layers.{i}.ff")
+    return ModelBlueprint(
+        hidden_size=H, vocab_size=cfg.vocab_size,
+        embedding=PartSpec("embedding", "token_table", dict(vocab_size=cfg.vocab_size, hidden_size=H), "t2.embed"),
+        positions={"rope": PartSpec("position", "rotary_half", dict(head_dim=16, theta=50.0, max_positions=128)),
+                   "sinus": PartSpec("position", "toy_sinusoid_table", dict(size=H, period=3.0, amp=0.5, max_positions=128))},
+        # different mixers AND different feed-forwards from layer to layer
+        layers=[layer(0, gate(0), routed(0)), layer(1, attn(1), routed(1)), layer(2, gate(2), dense(2))],
+        schedule=[RunSpec(0), RunSpec(1), RunSpec(2)],
+        final_norm=norm("t2.norm"),
+        head=PartSpec("head", "linear_head", dict(vocab_size=cfg.vocab_size, hidden_size=H, tied_to=None), "t2.head"),
+        max_positions=128)
+
+
+fd.register_architecture("Toy2ForCausalLM", Toy2Config, toy2_blueprint)
+
+
+def toy2_plain(w: Dict[str, torch.Tensor], cfg: Toy2Config, tokens: List[int]) -> torch.Tensor:
+    w = {k: v.double() for k, v in w.items()}
+    H, S = cfg.hidden_size, len(tokens)
+    x = w["t2.embed.weight"][torch.tensor(tokens)]
+    pos = torch.arange(S, dtype=torch.float32)[:, None]
+    table = (1.0 + 0.5 * torch.sin(pos / 3.0 + torch.arange(H, dtype=torch.float32)[None, :])).double()
+    cos, sin = P.rope_tables(16, S, 50.0)
+
+    def gate(i, h):
+        return (h * table) @ w[f"t2.layers.{i}.gate.weight"].T
+
+    def attn(i, h):
+        p = f"t2.layers.{i}.attn"
+        q = P.apply_rope(P.linear(h, w[f"{p}.q_proj.weight"]).view(S, 2, 16), cos, sin)
+        k = P.apply_rope(P.linear(h, w[f"{p}.k_proj.weight"]).view(S, 2, 16), cos, sin)
+        v = P.linear(h, w[f"{p}.v_proj.weight"]).view(S, 2, 16)
+        return P.linear(P.causal_gqa_attention(q, k, v, 0.25, None).reshape(S, 32), w[f"{p}.o_proj.weight"])
+
+    def routed(i, h):
+        choice = (h @ w[f"t2.layers.{i}.moe.router.weight"].T).argmax(-1)
+        experts = w[f"t2.layers.{i}.moe.experts.weight"].view(cfg.n_experts, H, H)
+        return torch.stack([experts[c] @ h[t] for t, c in enumerate(choice.tolist())])
+
+    def dense(i, h):
+        p = f"t2.layers.{i}.ff"
+        return P.linear(P.swiglu(P.linear(h, w[f"{p}.gate_proj.weight"]), P.linear(h, w[f"{p}.up_proj.weight"])),
+                        w[f"{p}.down_proj.weight"])
+
+    for i, (mix, ff) in enumerate([(gate, routed), (attn, routed), (gate, dense)]):
+        x = x + mix(i, P.rmsnorm(x, w[f"t2.layers.{i}.n1.weight"], cfg.eps))
+        x = x + ff(i, P.rmsnorm(x, w[f"t2.layers.{i}.n2.weight"], cfg.eps))
+    return P.rmsnorm(x, w["t2.norm.weight"], cfg.eps) @ w["t2.head.weight"].T
+
+
+def test_toy_routing_and_another_position_encoding(tmp_path):
+    """A feed-forward with routing, a position encoding that is not rotary, and layers that differ in both
+    mixer and feed-forward: registered here, built from config.json and stepped like any model (float32,
+    where the router's choice is the same as the plain implementation's)."""
+    cfg = Toy2Config(32, 77, 3, 1e-5)
+    folder = tmp_path / "toy2"
+    probe = Model.from_config(cfg, torch.float32, "cpu")
+    tensors = fd.weights.random_tensors(probe.tensor_specs(), 9, dtype=torch.float32)
+    # well separated router logits, so that rounding cannot change a choice
+    for k in tensors:
+        if k.endswith("router.weight"):
+            tensors[k] = tensors[k] * 40
+    fd.weights.write_model_folder(folder, cfg.to_dict(), tensors)
+    eng = fd.load(folder, device="cuda", dtype="float32")
+    model = eng.model
+    assert isinstance(model.blocks[0].feed_forward, Top1Experts) and isinstance(model.blocks[2].mixer, PositionGate)
+    assert len(model.cache_groups()) == 1 and model.cache_groups()[0].n_layers == 1      # only layer 1 keeps keys
+    cache = model.new_cache(max_tokens=256, block_size=8)
+    prompts = prompts_for(77, [19, 6, 33], seed=4)
+    want = [toy2_plain(tensors, cfg, p) for p in prompts]
+    slots = [cache.admit() for _ in prompts]
+    heads = [len(p) - 3 for p in prompts]
+    got = model.step(cache, slots, [p[:h] for p, h in zip(prompts, heads)], "all")
+    o = 0
+    for h, ref in zip(heads, want):
+        assert rel_err(got[o:o + h], ref[:h]) < 1e-4
+        o += h
+    for i in range(3):
+        got = model.step(cache, slots, [[p[h + i]] for p, h in zip(prompts, heads)], "last")
+        for j, ref in enumerate(want):
+            assert rel_err(got[j], ref[heads[j] + i]) < 1e-4
     model.check_status()
