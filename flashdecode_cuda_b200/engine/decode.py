@@ -22,6 +22,7 @@ import numpy as np
 import torch
 
 from .. import kernels as K
+from ..cache.allocator import PoolExhausted
 from ..cache.paged import PagedCache
 from .model import Model, StepContext, Workspace
 
@@ -89,11 +90,10 @@ class GraphDecoder:
         lens = [cache.length(s) for s in slots]
         if max(lens) + 1 > cache.max_len:
             raise ValueError(f"a sequence would grow beyond the cache's longest sequence {cache.max_len}")
-        toks = np.asarray(tokens, dtype=np.int64)
-        if toks.min() < 0 or toks.max() >= self.model.vocab_size:
+        if min(tokens) < 0 or max(tokens) >= self.model.vocab_size:       # plain integers: cheaper than array reductions
             raise ValueError(f"token ids must lie in [0, {self.model.vocab_size})")
         h = g.host
-        h[0:n] = toks
+        h[0:n] = tokens
         h[2 * B:2 * B + n] = lens               # positions of the new tokens
         h[3 * B:3 * B + n] = slots
         h[3 * B + n:4 * B] = -1
@@ -168,6 +168,14 @@ class GraphDecoder:
             cache.advance(s, 1)
         self.last, self.last_n = g, n
         self.launches_per_step = g.launches
+        # While the GPU runs this step: the blocks of the next one.  If every sequence goes on, the next call's
+        # reserve and sync find nothing to do; one that ends gives the block back with its slot.  A refusal
+        # here (a full pool, a sequence at its longest) is the next call's to report, if it still applies.
+        try:
+            cache.reserve([(s, 1) for s in slots])
+            cache.sync()
+        except (ValueError, PoolExhausted):
+            pass
         return g.sampled
 
     def read_tokens(self, n: int) -> List[int]:

@@ -75,11 +75,15 @@ class StepContext:
 
 class _Staging:
     """Ring of pinned host buffers for the per-step index upload; a buffer is
-    reused only after the copy that read it has completed."""
+    reused only after the copy that read it has completed.  The numpy views of
+    the buffers and the events are made once: this runs between two decode steps,
+    while the GPU has nothing to do."""
 
     def __init__(self, n: int = 4):
         self.bufs: List[Optional[torch.Tensor]] = [None] * n
+        self.views: List[Optional[np.ndarray]] = [None] * n
         self.events: List[Optional[torch.cuda.Event]] = [None] * n
+        self.used = [False] * n
         self.i = 0
 
     def upload(self, host: np.ndarray, dst: torch.Tensor) -> None:
@@ -88,17 +92,19 @@ class _Staging:
             return
         i = self.i
         self.i = (i + 1) % len(self.bufs)
-        if self.events[i] is not None:
+        if self.used[i]:
             self.events[i].synchronize()
+        n = host.size
         buf = self.bufs[i]
-        if buf is None or buf.numel() < host.size:
-            buf = torch.empty(max(host.size, 1024), dtype=torch.int32).pin_memory()
-            self.bufs[i] = buf
-        buf[:host.size].numpy()[:] = host
-        dst.copy_(buf[:host.size], non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
-        self.events[i] = ev
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
+            self.bufs[i], self.views[i] = buf, buf.numpy()
+            if self.events[i] is None:
+                self.events[i] = torch.cuda.Event()
+        self.views[i][:n] = host
+        dst.copy_(buf[:n], non_blocking=True)
+        self.events[i].record()
+        self.used[i] = True
 
 
 class Model:
