@@ -17,6 +17,13 @@ constexpr int DM_TILE = 16;       // keys per warp tile
 constexpr int DM_STAGES = 3;     // tiles of a warp under way or in use: two loads always in flight
 
 
+// 2^x by the special function unit (two units in the last place; 2^-inf = 0)
+__device__ __forceinline__ float dm_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // barriers of a group: the whole CTA, or 128 threads of it that share the named barrier `id` (1..15)
 struct CtaSync {
     __device__ __forceinline__ void operator()() const { __syncthreads(); }
@@ -113,6 +120,26 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
     };
     fetch_blocks(0);
 
+    // Per-lane constants of the main loop (an address then costs one add): where this lane's 16-byte chunks of
+    // a tile go in shared memory, and where its ldmatrix rows of K and of V start.
+    uint32_t chunk_off[DM_TILE * CPR / 32];
+#pragma unroll
+    for (int u = 0; u < DM_TILE * CPR / 32; ++u) {
+        const int c = u * 32 + lane;
+        chunk_off[u] = (uint32_t)swz<D>(c / CPR, c % CPR);
+    }
+    uint32_t k_off[D / 16], v_off[D / 16];
+    {
+        const int mi = lane >> 3;
+        const int rk = (mi >> 1) * 8 + (lane & 7), rv = (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            k_off[kk] = (uint32_t)swz<D>(rk, kk * 2 + (mi & 1));
+            v_off[kk] = (uint32_t)swz<D>(rv, kk * 2 + (mi >> 1));
+        }
+    }
+    const uint32_t my_u32 = smem_u32(my);
+
     // stage the warp's i-th 16-key tile (keys and values); called with i ascending
     auto issue = [&](int i, int stage) {
         const int j = warp + i * DM_WARPS;
@@ -127,15 +154,15 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
             if (t0 >= lo && t0 + DM_TILE <= hi && tile_blk >= 0 && tile_blk < p.num_blocks) {
                 // the usual case, a whole tile inside one block: one base address, constant offsets per lane
                 // (the address arithmetic of the general path below cost more than the tile's tensor work)
-                const size_t base = (((size_t)tile_blk * p.n_kv + kvh) * bs + tile_off) * D;
+                // the tile is DM_TILE * D contiguous elements in each pool: chunk c of the tile lies 16 c bytes in
+                const size_t base = (((size_t)tile_blk * p.n_kv + kvh) * bs + tile_off) * D + lane * 8;
                 const __nv_bfloat16* kb = kp + base;
                 const __nv_bfloat16* vb = vp + base;
+                const uint32_t ks32 = my_u32 + stage * 2 * TILE_BYTES, vs32 = ks32 + TILE_BYTES;
 #pragma unroll
                 for (int u = 0; u < DM_TILE * CPR / 32; ++u) {
-                    const int c = u * 32 + lane;
-                    const int r = c / CPR, cc = c - r * CPR;
-                    cp_async16(smem_u32(ks + swz<D>(r, cc)), kb + r * D + cc * 8, 16);
-                    cp_async16(smem_u32(vs + swz<D>(r, cc)), vb + r * D + cc * 8, 16);
+                    cp_async16(ks32 + chunk_off[u], kb + u * 256, 16);
+                    cp_async16(vs32 + chunk_off[u], vb + u * 256, 16);
                 }
                 cp_async_commit();
                 return;
@@ -198,52 +225,52 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
         // refill the stage that iteration i - 1 finished with
         if (i + DM_STAGES - 1 < n_mine) issue(i + DM_STAGES - 1, (i + DM_STAGES - 1) % DM_STAGES);
         else cp_async_commit();
-        const unsigned char* ks = my + (i % DM_STAGES) * 2 * TILE_BYTES;
-        const unsigned char* vs = ks + TILE_BYTES;
+        const uint32_t ks32 = my_u32 + (i % DM_STAGES) * 2 * TILE_BYTES, vs32 = ks32 + TILE_BYTES;
 
         // S = Q K^T for 16 keys: two n-tiles of 8 keys
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        {
-            const int mi = lane >> 3;
-            const int r = (mi >> 1) * 8 + (lane & 7);            // key row of this lane's matrix
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4(smem_u32(ks + swz<D>(r, kk * 2 + (mi & 1))), b0, b1, b2, b3);
-                uint32_t a0, a1, a2, a3;
-                if (QREG) { a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3]; }
-                else ldmatrix_x4(smem_u32(q_s + swz<D>(q_r, kk * 2 + (q_mi >> 1))), a0, a1, a2, a3);
-                mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
-                mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
-            }
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(ks32 + k_off[kk], b0, b1, b2, b3);
+            uint32_t a0, a1, a2, a3;
+            if (QREG) { a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3]; }
+            else ldmatrix_x4(smem_u32(q_s + swz<D>(q_r, kk * 2 + (q_mi >> 1))), a0, a1, a2, a3);
+            mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
+            mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
         }
-        // mask and online softmax (base 2); this thread's keys: t0 + (lane%4)*2 + {0,1} (+8)
+        // mask and online softmax (base 2, the maximum kept in units of the raw scores: scale > 0);
+        // this thread's keys: t0 + (lane%4)*2 + {0,1} (+8).  Only a split's first and last tile can hold
+        // keys outside [lo, hi).
         const int t0 = (first_tile + j) * DM_TILE;
-        float mx[2] = {-INFINITY, -INFINITY};
+        if (t0 < lo || t0 + DM_TILE > hi) {
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+            for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int t = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                const float v = (t >= lo && t < hi) ? s[nt][e] * scale_log2 : -INFINITY;
-                s[nt][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
-        float alpha[2];
+                for (int e = 0; e < 4; ++e) {
+                    const int t = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    if (t < lo || t >= hi) s[nt][e] = -INFINITY;
+                }
+        }
+        float mx[2];
+        mx[0] = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx[1] = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        float alpha[2], m_off[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
             const float m_new = fmaxf(m_run[h], mx[h]);
-            alpha[h] = m_new == -INFINITY ? 1.f : exp2f(m_run[h] - m_new);
+            alpha[h] = m_new == -INFINITY ? 1.f : dm_ex2((m_run[h] - m_new) * scale_log2);   // m_run = -inf: 0
             m_run[h] = m_new;
+            m_off[h] = m_new == -INFINITY ? 0.f : m_new * scale_log2;                        // all masked so far: P = 2^-inf = 0
         }
         float rs[2] = {0.f, 0.f};
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float pv = m_run[e >> 1] == -INFINITY ? 0.f : exp2f(s[nt][e] - m_run[e >> 1]);
+                const float pv = dm_ex2(fmaf(s[nt][e], scale_log2, -m_off[e >> 1]));
                 s[nt][e] = pv;
                 rs[e >> 1] += pv;
             }
@@ -253,22 +280,18 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
         const uint32_t pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
         // O = O * alpha + P V
         const bool rescale = __any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f);
-        {
-            const int mi = lane >> 3;
-            const int r = (mi & 1) * 8 + (lane & 7);             // key row
 #pragma unroll
-            for (int np = 0; np < D / 16; ++np) {
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(smem_u32(vs + swz<D>(r, np * 2 + (mi >> 1))), b0, b1, b2, b3);
-                float* oa = o[np * 2];
-                float* ob = o[np * 2 + 1];
-                if (rescale) {       // most tiles leave every running maximum as it was
-                    oa[0] *= alpha[0]; oa[1] *= alpha[0]; oa[2] *= alpha[1]; oa[3] *= alpha[1];
-                    ob[0] *= alpha[0]; ob[1] *= alpha[0]; ob[2] *= alpha[1]; ob[3] *= alpha[1];
-                }
-                mma_bf16(oa, pa0, pa1, pa2, pa3, b0, b1);
-                mma_bf16(ob, pa0, pa1, pa2, pa3, b2, b3);
+        for (int np = 0; np < D / 16; ++np) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(vs32 + v_off[np], b0, b1, b2, b3);
+            float* oa = o[np * 2];
+            float* ob = o[np * 2 + 1];
+            if (rescale) {       // most tiles leave every running maximum as it was
+                oa[0] *= alpha[0]; oa[1] *= alpha[0]; oa[2] *= alpha[1]; oa[3] *= alpha[1];
+                ob[0] *= alpha[0]; ob[1] *= alpha[0]; ob[2] *= alpha[1]; ob[3] *= alpha[1];
             }
+            mma_bf16(oa, pa0, pa1, pa2, pa3, b0, b1);
+            mma_bf16(ob, pa0, pa1, pa2, pa3, b2, b3);
         }
         __syncwarp();      // every lane is done with this stage before it is refilled
     }
@@ -306,7 +329,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
 #pragma unroll
         for (int w = 0; w < DM_WARPS; ++w) {
             const float mw = m_s[w * 16 + r];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+            const float f = mw == -INFINITY ? 0.f : exp2f((mw - m) * scale_log2);      // the maxima are raw scores
             l += l_s[w * 16 + r] * f;
             a += reinterpret_cast<const float*>(kv_s + w * WARP_BYTES)[r * D + j] * f;
         }
@@ -314,7 +337,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
         if (p.n_splits > 1) {
             const size_t pi = row * p.n_splits + split;
             p.part_acc[pi * D + j] = a;
-            if (j == 0) { p.part_m[pi] = m * LN2; p.part_l[pi] = l; }   // natural-log units for the merge
+            if (j == 0) { p.part_m[pi] = m * scale_log2 * LN2; p.part_l[pi] = l; }   // natural-log units for the merge
         } else {
             static_cast<__nv_bfloat16*>(p.out)[row * D + j] = __float2bfloat16_rn(l > 0.f ? a / l : 0.f);
         }
