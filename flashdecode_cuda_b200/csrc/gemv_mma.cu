@@ -179,7 +179,7 @@ static int run_gemv(GemvParams& p, const RopeArgs& ra, cudaStream_t stream) {
     const int nt = p.M <= 8 ? 1 : (p.M <= 16 ? 2 : (p.M <= 32 ? 4 : 8));
     switch (nt) {
         case 1: return launch_gemv_wk<1, 8>(p, ra, stream);
-        case 2: return launch_gemv_wk<2, 4>(p, ra, stream);
+        case 2: return launch_gemv_wk<2, 8>(p, ra, stream);     // 8 chunks in flight as well: 13.5 against 20.6 us for gate/up at 16 rows
         case 4: return launch_gemv_wk<4, 2>(p, ra, stream);
         default: return launch_gemv_wk<8, 1>(p, ra, stream);
     }
