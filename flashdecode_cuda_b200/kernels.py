@@ -143,8 +143,8 @@ def require_device() -> None:
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch for this library's kernels: a kernel may start, and fetch
     weights, while the previous one is still finishing.  Off by default: measured on B200 inside
-    the captured decode graph it was 2-7 % slower than plain stream order (the early CTAs hold SM
-    slots while they wait)."""
+    the captured decode graph every programmatic edge made the step slower (all kernels: 2.34
+    against 1.46 ms at batch 8; a single kind of product per layer: 1.50 to 1.62 ms)."""
     lib().fd_set_pdl(int(on))
 
 
