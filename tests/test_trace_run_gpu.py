@@ -57,10 +57,14 @@ def build_trace(reqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_replay(tmp_path, dtype):
-    folder = write_folder(tmp_path, "C", seed=9)
-    V = TINY["C"]["vocab_size"]
-    reqs = prompts_for(V, [40, 75, 33], seed=12)
+@pytest.mark.parametrize("name,lengths", [("C", [40, 75, 33]), ("E", [140, 300, 70])])
+def test_replay(tmp_path, dtype, name, lengths):
+    """C: odd sizes (the CUDA-core attention in both dtypes).  E: head size 128, a window on one layer and
+    prompts longer than a 128-row tile (in bfloat16 the tcgen05 products and attention, the tensor-core decode
+    attention and the weight-streaming decode products)."""
+    folder = write_folder(tmp_path, name, seed=9)
+    V = TINY[name]["vocab_size"]
+    reqs = prompts_for(V, lengths, seed=12)
     steps, expect = build_trace(reqs)
     out_dir = tmp_path / f"out_{dtype}"
     # live tokens at any time: at most three requests, each rounded up to a multiple of 64
