@@ -82,8 +82,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // Bounded wait for the phase with the given parity.  False: the time ran out (or another
 // thread already gave up); the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    const unsigned long long t0 = global_ns();
-    for (;;) {
+    unsigned long long t0 = 0;
+    for (uint32_t spins = 0;; ++spins) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -91,8 +91,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
+        if ((spins & 63) != 63) continue;                    // the clock and the flag only now and then
         if (*abort_flag) return false;
-        if (global_ns() - t0 > TC_WAIT_NS) {
+        if (t0 == 0) t0 = global_ns();
+        else if (global_ns() - t0 > TC_WAIT_NS) {
             *abort_flag = 1;
             set_status(status, STATUS_WAIT_TIMEOUT);
             return false;
@@ -544,6 +546,190 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     }
 }
 
+// ---- the two-SM form ---------------------------------------------------------
+// A cluster of two CTAs (two SMs) computes one 256 x 256 tile with tcgen05.mma.cta_group::2: each CTA holds
+// 128 rows of x and HALF of the W tile (128 of its 256 rows) in its own shared memory and gets 128 rows of the
+// accumulator in its own tensor memory; the tensor cores of both SMs read both halves of W.  A stage is then
+// 32 KB per CTA instead of 48 KB for the same 4 MFLOP per CTA, so six stages fit and the copies from L2 keep up
+// (the wide one-SM form above waits for data more than half of the time).
+//  * both CTAs run a TMA thread; every copy signals the LEADER's (rank 0) `full` barrier, which expects the
+//    bytes of both CTAs (cp.async.bulk.tensor with .cta_group::2 may signal the peer's barrier);
+//  * the leader's MMA thread issues for the pair; tcgen05.commit with a CTA mask hands a stage back to both
+//    TMA threads and an accumulator to both CTAs' epilogue warps;
+//  * both CTAs' epilogue warps read their own tensor memory and arrive (the peer remotely) on the leader's
+//    `acc_empty` barrier; tensor memory is allocated and freed by one warp of each CTA together.
+constexpr int TP_STAGES = 6;
+constexpr int TP_B_BYTES = 128 * TC_BK * 2;                   // this CTA's half of the W tile: 16 KB
+constexpr int TP_STAGE_BYTES = TC_A_BYTES + TP_B_BYTES;       // 32 KB
+constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the shared::cluster address of the same variable in the CTA of the given rank
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+__global__ void __launch_bounds__(TW_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         const TcParams p, const TcRope ra, const int tiles_m, const int tiles_n) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TP_STAGES * TP_STAGE_BYTES);
+    uint64_t* full = bars;                       // [S] used in the leader: both CTAs' copies of a stage have landed
+    uint64_t* empty = bars + TP_STAGES;          // [S] in each CTA: the MMAs that read the stage are done
+    uint64_t* acc_full = bars + 2 * TP_STAGES;   // [2] in each CTA: an accumulator is complete
+    uint64_t* acc_empty = acc_full + 2;          // [2] used in the leader: both CTAs' epilogue warps have read it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    const int n_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag[0] = 0;
+        abort_flag[1] = 0;
+        for (int s = 0; s < TP_STAGES; ++s) {
+            mbar_init(s_addr(&full[s]), 1);
+            mbar_init(s_addr(&empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s_addr(&acc_full[b]), 1);
+            mbar_init(s_addr(&acc_empty[b]), 2 * TW_EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // one warp of each CTA, together: the same 512 columns in both tensor memories
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();              // the peer's barriers exist before anything of this CTA signals them
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer (in both CTAs): this CTA's 128 rows of x and its half of the W tile ----
+        int it = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < n_tiles; tile += n_pairs) {
+            const int m0 = (tile % tiles_m) * (2 * TC_BM) + (int)rank * TC_BM;
+            const int n0 = (tile / tiles_m) * TW_BN + (int)rank * TC_BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % TP_STAGES;
+                if (it >= TP_STAGES && !mbar_wait(s_addr(&empty[s]), ((it / TP_STAGES) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                if (*abort_flag) { ok = false; break; }
+                if (leader) mbar_expect_tx(s_addr(&full[s]), 2 * TP_STAGE_BYTES);
+                const uint32_t fb = map_to_rank(s_addr(&full[s]), 0);
+                unsigned char* a = tiles + s * TP_STAGE_BYTES;
+                tma_load_2d_pair(s_addr(a), &map_x, fb, k * TC_BK, m0);
+                tma_load_2d_pair(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);
+            }
+        }
+        // Giving up: the copies in flight must land before this CTA's shared memory goes away.  The leader sees
+        // them on its own barriers; the peer cannot wait on the leader's, so it waits out the copies' time.
+        if (*abort_flag) {
+            if (leader) {
+                for (int j = max(0, it - TP_STAGES); j < it; ++j)
+                    mbar_wait(s_addr(&full[j % TP_STAGES]), (j / TP_STAGES) & 1, abort_flag + 1, nullptr);
+            } else {
+                const unsigned long long t0 = global_ns();
+                while (global_ns() - t0 < 1000000ull) { }
+            }
+        }
+    } else if (warp == 1 && lane == 0 && leader) {
+        // ---- MMA issuer, for the pair: M 256 (128 rows in each CTA), N 256 ----
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TW_BN >> 3) << 17) | ((uint32_t)((2 * TC_BM) >> 4) << 24);
+        int it = 0, t = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < n_tiles; tile += n_pairs, ++t) {
+            const int buf = t & 1;
+            if (t >= 2 && !mbar_wait(s_addr(&acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t acc = tmem + buf * TW_BN;
+            for (int k = 0; k < k_iters; ++k, ++it) {
+                const int s = it % TP_STAGES;
+                if (!mbar_wait(s_addr(&full[s]), (it / TP_STAGES) & 1, abort_flag, p.status)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a = s_addr(tiles + s * TP_STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)
+                    tc_mma_pair(acc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0);
+                tc_commit_pair(s_addr(&empty[s]), 3);          // the stage is free in both CTAs
+            }
+            if (ok) tc_commit_pair(s_addr(&acc_full[buf]), 3); // the accumulator is complete in both CTAs
+        }
+        if (!ok || *abort_flag) { tc_commit_pair(s_addr(&acc_full[0]), 3); tc_commit_pair(s_addr(&acc_full[1]), 3); }
+    } else if (warp >= 2) {
+        // ---- epilogue (in both CTAs): this CTA's 128 rows of the tile ----
+        const int quarter = warp & 3;
+        const int col_half = (warp - 2) >> 2;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        int t = 0;
+        for (int tile = pair; tile < n_tiles; tile += n_pairs, ++t) {
+            const int buf = t & 1;
+            const int m0 = (tile % tiles_m) * (2 * TC_BM) + (int)rank * TC_BM, n0 = (tile / tiles_m) * TW_BN;
+            const int m = m0 + quarter * 32 + lane;
+            const TcToken tk = tc_token(p, ra, m);
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status)) &&
+                            *abort_flag == 0;
+            if (!__all_sync(0xffffffffu, ok)) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c0 = col_half * (TW_BN / 2); c0 < (col_half + 1) * (TW_BN / 2); c0 += 32) {
+                uint32_t v[32];
+                tc_ld32(tmem + lane_base + buf * TW_BN + c0, v);
+                tc_wait_ld();
+                tc_store32(p, ra, tk, v, m, n0 + c0);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(s_addr(&acc_empty[buf]), 0));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();              // neither CTA leaves (or frees tensor memory) while the other may still touch it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
 // ---- host side ------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -590,7 +776,7 @@ static int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out, int
     return 0;
 }
 
-int g_tc_wide = 1;      // 1: the wide persistent kernel where N >= 256; 0: always 128 x 128 tiles, one per CTA
+int g_tc_wide = 1;      // 2: the two-SM kernel where N >= 256; 1: the wide one-SM kernel; 0: 128 x 128 tiles, one per CTA
 
 static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRope& ra, cudaStream_t stream,
                      const char* what) {
@@ -599,6 +785,7 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TW_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM);
         if (e != cudaSuccess) return fail(-3, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", TW_SMEM, cudaGetErrorString(e));
         int dev = 0;
         cudaGetDevice(&dev);
@@ -610,8 +797,17 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
     CUtensorMap mx, mw;
     int rc = tensor_map(x, p.M, p.K, &mx);
     if (rc != 0) return rc;
-    rc = tensor_map(w, p.N, p.K, &mw, wide ? TW_BN : TC_BM);
+    const bool pair = wide && g_tc_wide == 2;
+    rc = tensor_map(w, p.N, p.K, &mw, (wide && !pair) ? TW_BN : TC_BM);
     if (rc != 0) return rc;
+    if (pair) {
+        const int tiles_m2 = (p.M + 2 * TC_BM - 1) / (2 * TC_BM), tiles_n = (p.N + TW_BN - 1) / TW_BN;
+        const long long n_tiles = (long long)tiles_m2 * tiles_n;
+        FD_REQUIRE(n_tiles < (1ll << 30), -2, "gemm_tcgen05: %lld tiles", n_tiles);
+        const int pairs = (int)(n_tiles < sms / 2 ? n_tiles : sms / 2);
+        return launch(what, gemm_tcgen05_pair_kernel, dim3(2 * pairs), dim3(TW_THREADS), TP_SMEM, stream, dim3(2, 1, 1), mx, mw, p, ra,
+                      tiles_m2, tiles_n);
+    }
     if (wide) {
         const int tiles_n = (p.N + TW_BN - 1) / TW_BN;
         const long long n_tiles = (long long)tiles_m * tiles_n;
@@ -633,7 +829,7 @@ using namespace fd;
 // Which tiling the products use from now on (1: wide persistent kernel where N >= 256, the default;
 // 0: 128 x 128 tiles only).  For tests and measurements.
 extern "C" int fd_gemm_tc_set_wide(int on) {
-    g_tc_wide = on ? 1 : 0;
+    g_tc_wide = on < 0 ? 0 : (on > 2 ? 2 : on);
     return 0;
 }
 

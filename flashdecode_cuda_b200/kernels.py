@@ -242,10 +242,10 @@ def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
 GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
 
 
-def gemm_tc_set_wide(on: bool) -> None:
-    """Which tiling ``gemm_tc`` and ``gemm_tc_qkv_rope`` use from now on: the persistent kernel with
-    128 x 256 tiles and a double-buffered accumulator where N >= 256 (the default), or 128 x 128
-    tiles, one per CTA, everywhere.  For tests and measurements."""
+def gemm_tc_set_wide(on) -> None:
+    """Which tiling ``gemm_tc`` and ``gemm_tc_qkv_rope`` use from now on where N >= 256: 2 = two SMs per
+    256 x 256 tile (``tcgen05.mma.cta_group::2``), 1 / True = one persistent CTA per SM with 128 x 256
+    tiles, 0 / False = 128 x 128 tiles, one per CTA, everywhere.  For tests and measurements."""
     lib().fd_gemm_tc_set_wide(int(on))
 
 

@@ -201,12 +201,16 @@ def test_gemv_refuses_what_it_cannot_do():
                torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV), K.GEMV_BF16)
 
 
-@pytest.fixture(params=[True, False], ids=["wide", "square"])
+TC_DEFAULT_TILING = 1
+
+
+@pytest.fixture(params=[2, 1, 0], ids=["pair", "wide", "square"])
 def tc_tiling(request):
-    """Both tilings of the tcgen05 product: 128 x 256 persistent (N >= 256) and 128 x 128."""
+    """The tilings of the tcgen05 product: two SMs per 256 x 256 tile, 128 x 256 persistent (both for
+    N >= 256) and 128 x 128."""
     K.gemm_tc_set_wide(request.param)
     yield request.param
-    K.gemm_tc_set_wide(True)
+    K.gemm_tc_set_wide(TC_DEFAULT_TILING)
 
 
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (128, 256, 256), (130, 200, 72), (70, 333, 1536), (2048, 2048, 1536),
