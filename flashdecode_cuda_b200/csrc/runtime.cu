@@ -52,3 +52,12 @@ extern "C" int fd_set_pdl(int on) {
     fd::g_pdl = on ? 1 : 0;
     return 0;
 }
+
+// One asynchronous copy from pinned host memory to the device on the given stream (the per-step index
+// array of a decode step; a plain call costs a fraction of a tensor-library copy on the host).
+extern "C" int fd_copy_h2d_async(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+    if (bytes <= 0) return 0;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream);
+    if (e != cudaSuccess) return fd::fail(-100, "copy to the device failed: %s", cudaGetErrorString(e));
+    return 0;
+}

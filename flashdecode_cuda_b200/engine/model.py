@@ -102,7 +102,7 @@ class _Staging:
             if self.events[i] is None:
                 self.events[i] = torch.cuda.Event()
         self.views[i][:n] = host
-        dst.copy_(buf[:n], non_blocking=True)
+        K.copy_h2d_async(dst, buf, n)
         self.events[i].record()
         self.used[i] = True
 

@@ -92,6 +92,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
+        "fd_copy_h2d_async": [P, P, LL, P],
         "fd_decode_stack_layer_bytes": [],
         "fd_decode_stack_params_bytes": [],
         "fd_decode_stack_plan": [I, I, I, I],
@@ -146,6 +147,13 @@ def set_pdl(on: bool) -> None:
     the captured decode graph every programmatic edge made the step slower (all kernels: 2.34
     against 1.46 ms at batch 8; a single kind of product per layer: 1.50 to 1.62 ms)."""
     lib().fd_set_pdl(int(on))
+
+
+def copy_h2d_async(dst: torch.Tensor, src_pinned: torch.Tensor, n_elements: int) -> None:
+    """dst[:n] <- src[:n] from pinned host memory, asynchronously on the current stream."""
+    rc = lib().fd_copy_h2d_async(dst.data_ptr(), src_pinned.data_ptr(), n_elements * dst.element_size(), _stream())
+    if rc != 0:
+        raise KernelError(lib().fd_last_error().decode())
 
 
 def sm_count() -> int:
