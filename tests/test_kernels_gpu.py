@@ -708,3 +708,74 @@ def test_sample_temperature_follows_the_distribution():
     freq = torch.bincount(out.cpu().long(), minlength=5).double() / n
     want = torch.softmax(logits[0].double() / 0.7, 0)
     assert float((freq - want).abs().max()) < 0.03
+
+
+# ---------------------------------------------------------------------------
+# drawn shapes: what the hand-picked cases above may have missed
+# ---------------------------------------------------------------------------
+def test_attention_prompts_drawn_shapes():
+    """Prompt steps at head size 128 with drawn group sizes, block sizes, cached prefixes, prompt lengths
+    around the 128- and 256-row tiles and windows (the tcgen05 kernel, and the decode kernel where every
+    sequence brings one token)."""
+    import random
+    rnd = random.Random(11)
+    for case in range(40):
+        n_kv = rnd.choice([1, 2, 3])
+        n_q = n_kv * rnd.choice([1, 2, 3, 6])
+        bs = rnd.choice([8, 16, 32, 64, 128])
+        n_seq = rnd.randint(1, 4)
+        ctx = [rnd.choice([0, 0, rnd.randint(1, 300)]) for _ in range(n_seq)]
+        new = [rnd.choice([1, rnd.randint(2, 127), 128, 129, 255, 256, 257, rnd.randint(130, 600)]) for _ in range(n_seq)]
+        window = rnd.choice([0, 0, 1, rnd.randint(2, 700), 64, 128, 256])
+        got, want, _ = run_attention("bfloat16", n_q, n_kv, 128, bs, ctx=ctx, new=new, window=window, fn=K.attention,
+                                     seed=case)
+        assert rel(got, want) < TOL["bfloat16"], dict(n_q=n_q, n_kv=n_kv, bs=bs, ctx=ctx, new=new, window=window)
+
+
+def test_attention_decode_drawn_shapes():
+    """Decode steps on the tensor-core kernel with drawn head sizes, groups, block sizes (also below a
+    16-key tile and no power of two), lengths, windows and splits of the keys."""
+    import random
+    rnd = random.Random(12)
+    for case in range(60):
+        d = rnd.choice([64, 128])
+        n_kv = rnd.choice([1, 2, 4])
+        n_q = n_kv * rnd.choice([1, 2, 3, 6, 7, 16])
+        bs = rnd.choice([1, 4, 8, 16, 32, 64, 48])
+        n_seq = rnd.randint(1, 6)
+        ctx = [rnd.choice([0, rnd.randint(1, 40), rnd.randint(41, 900)]) for _ in range(n_seq)]
+        window = rnd.choice([0, 0, 1, rnd.randint(2, 900), 16, 128])
+        n_splits = rnd.choice([1, 2, 3, 5, 8, 16, 17, 32])
+        split_len = 0
+        if n_splits > 1:
+            split_len = -(-(-(-(max(ctx) + 1) // n_splits)) // 32) * 32 + rnd.choice([0, 32])
+        got, want, _ = run_attention("bfloat16", n_q, n_kv, d, bs, ctx=ctx, new=[1] * n_seq, window=window,
+                                     n_splits=n_splits, split_len=split_len, pad_rows=rnd.choice([0, 2]),
+                                     fn=K.attention, seed=case)
+        assert rel(got, want) < TOL["bfloat16"], dict(d=d, n_q=n_q, n_kv=n_kv, bs=bs, ctx=ctx, window=window,
+                                                      n_splits=n_splits, split_len=split_len)
+
+
+def test_gemm_tcgen05_drawn_shapes():
+    """The three tilings of the tcgen05 product at drawn M, N, K: around the tile edges, fewer rows than one
+    CTA of a pair holds, N between one and two wide tiles, K that is no multiple of the 64-wide stage."""
+    import random
+    rnd = random.Random(13)
+    st = status()
+    try:
+        for case in range(45):
+            M = rnd.choice([1, 17, 127, 128, 129, 255, 256, 257, 300, 512, 1000, rnd.randint(1, 2500)])
+            N = rnd.choice([16, 256, 272, 384, 511, 512, 528, 1536, 2048, rnd.randint(1, 300) * 16])
+            K_ = rnd.choice([8, 64, 72, 128, 200, 1536, rnd.randint(1, 200) * 8])
+            tiling = case % 3
+            K.gemm_tc_set_wide(tiling)
+            g = torch.Generator().manual_seed(case)
+            x = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+            w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16).to(DEV)
+            b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+            K.gemm_tc(x, w, b, out, status=st)
+            assert rel(out, P.linear(x.double(), w.double()) + b.double()) < 5e-3, (M, N, K_, tiling)
+        assert int(st.item()) == 0
+    finally:
+        K.gemm_tc_set_wide(TC_DEFAULT_TILING)
