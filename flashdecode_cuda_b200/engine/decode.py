@@ -64,6 +64,7 @@ class GraphDecoder:
         self.last_n = 0
         self.launches_per_step = 0
         self._host_out: Optional[torch.Tensor] = None
+        self._ahead: Optional[Tuple] = None          # (graph, slots) whose next lengths are in the graph's index array already
 
     # ------------------------------------------------------------------
     def _key(self, n: int, longest: int, greedy: bool, seed: int) -> Tuple:
@@ -86,19 +87,26 @@ class GraphDecoder:
         """Re-upload the index array of a captured graph for a new step: the batch-shape parts
         (rows of tokens, counts, wanted rows) never change; tokens, slots and lengths do."""
         B, n = key[0], len(slots)
-        cache = self.cache
-        lens = [cache.length(s) for s in slots]
-        if max(lens) + 1 > cache.max_len:
-            raise ValueError(f"a sequence would grow beyond the cache's longest sequence {cache.max_len}")
         if min(tokens) < 0 or max(tokens) >= self.model.vocab_size:       # plain integers: cheaper than array reductions
             raise ValueError(f"token ids must lie in [0, {self.model.vocab_size})")
         h = g.host
         h[0:n] = tokens
+        ahead, self._ahead = self._ahead, None
+        if ahead is None or ahead[0] is not g or ahead[1] != tuple(slots):
+            self._fill_lengths(g, B, slots)     # else: written while the GPU ran the step before
+        self.model._staging.upload(h, g.meta)
+
+    def _fill_lengths(self, g: _Graph, B: int, slots: Sequence[int]) -> None:
+        """The slots and lengths of the next step into a graph's index array."""
+        n, cache = len(slots), self.cache
+        lens = [cache.length(s) for s in slots]
+        if max(lens) + 1 > cache.max_len:
+            raise ValueError(f"a sequence would grow beyond the cache's longest sequence {cache.max_len}")
+        h = g.host
         h[2 * B:2 * B + n] = lens               # positions of the new tokens
         h[3 * B:3 * B + n] = slots
         h[3 * B + n:4 * B] = -1
         h[6 * B:6 * B + n] = lens               # tokens cached before the step
-        self.model._staging.upload(h, g.meta)
 
     def _graph_for(self, key: Tuple, slots, tokens) -> Tuple[_Graph, StepContext]:
         g = self.graphs.get(key)
@@ -171,9 +179,14 @@ class GraphDecoder:
         # While the GPU runs this step: the blocks of the next one.  If every sequence goes on, the next call's
         # reserve and sync find nothing to do; one that ends gives the block back with its slot.  A refusal
         # here (a full pool, a sequence at its longest) is the next call's to report, if it still applies.
+        # The same for the index array: everything but the tokens, in case the same sequences go on with this graph.
+        self._ahead = None
         try:
             cache.reserve([(s, 1) for s in slots])
             cache.sync()
+            if g.host is not None and n == g.n_rows_real:
+                self._fill_lengths(g, key[0], slots)
+                self._ahead = (g, tuple(slots))
         except (ValueError, PoolExhausted):
             pass
         return g.sampled
