@@ -42,6 +42,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+BLOCK_SIZE = int(os.environ.get("FD_BLOCK_SIZE", "64"))      # tokens of a cache block (the library's default)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -143,7 +144,7 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
     vocab = model.vocab_size
     lo, hi = prompt_range or (context // 4, context // 2)
     prompts = ragged_prompts(batch, lo, hi, vocab, seed)
-    cache = model.new_cache(batch_size=batch, max_len=context, block_size=16)
+    cache = model.new_cache(batch_size=batch, max_len=context, block_size=BLOCK_SIZE)
     out = {}
     if e2e:
         # the public entry point: host token ids in, host token ids out, every step
@@ -200,7 +201,7 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
 def prefill_run(engine, cfg, tokens: int, warmup: int, seed: int, pk: dict):
     import torch
     model = engine.model
-    cache = model.new_cache(batch_size=1, max_len=tokens, block_size=16)
+    cache = model.new_cache(batch_size=1, max_len=tokens, block_size=BLOCK_SIZE)
     (prompt,) = ragged_prompts(1, tokens, tokens, model.vocab_size, seed)
     times = []
     for i in range(warmup + 3):
@@ -295,7 +296,7 @@ def main() -> int:
             "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "global_batch": args.batch, "seq_len": args.context, "prompt_lens": "uniform[%d,%d]" % prange,
-            "mean_context": round(main_run["mean_context"], 1), "block_size": 16, "parallelism": "1 GPU",
+            "mean_context": round(main_run["mean_context"], 1), "block_size": BLOCK_SIZE, "parallelism": "1 GPU",
             "l2": "each step reads %.2f GB, far beyond the 126 MB L2; no flush needed" % (step_bytes / 1e9),
             "peaks": pk["source"],
         },

@@ -55,7 +55,7 @@ constexpr int TA_QTILE = 2 * TA_QSLAB;    // Q [128][128]
 constexpr int TA_PTILE = TA_QSLAB;        // P [128][64]
 constexpr int TA_KTILE = 2 * TA_KSLAB;    // K or V [64][128]
 // 192 KB + barriers, one CTA per SM: two query tiles (Q 32 KB and P 16 KB each) and three key/value tiles
-// in flight (32 KB each)
+// in flight (32 KB each); with one query tile per CTA (see the kernel), one Q and four key/value tiles
 constexpr int TA_SMEM = TA_NQ * (TA_QTILE + TA_PTILE) + TA_STAGES * 2 * TA_KTILE + 256;
 constexpr unsigned long long TA_WAIT_NS = 200ull * 1000 * 1000;
 
@@ -147,18 +147,30 @@ __device__ __forceinline__ uint64_t ta_desc_mn(uint32_t addr, uint32_t slab_byte
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
+// SPLIT: the CTA takes 128 query tokens only, and its two groups of softmax warps work on the SAME query tile:
+// the first on the even key tiles of its range, the second on the odd ones, each with its own running maximum,
+// sum and O; at the end the second group hands its state over through shared memory and the first adds the two
+// up.  A query tile's chain of key tiles - what bounds the time of a short prompt, whose few CTAs do not fill
+// the GPU - is half as long this way; every key tile is then used by one group only, which a long prompt pays
+// for in shared-memory and L2 traffic, so the launcher picks this form only while the other leaves SMs idle.
+template <bool SPLIT>
 __global__ void __launch_bounds__(TA_THREADS, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+    // SPLIT: one copy of the one query tile, and the 32 KB that saves as a fourth key/value tile in flight
+    constexpr int STAGES = SPLIT ? TA_STAGES + 1 : TA_STAGES;
+    constexpr int NQB = SPLIT ? 1 : TA_NQ;
+    static_assert(NQB * TA_QTILE + TA_NQ * TA_PTILE + STAGES * 2 * TA_KTILE + 256 <= TA_SMEM, "shared memory layout");
+    static_assert(STAGES * 2 * TA_KTILE >= (TA_D + 2) * TA_BM * 4, "the ring takes the second group's O, maxima and sums");
     extern __shared__ __align__(1024) unsigned char ta_raw[];
     unsigned char* q_s = ta_raw;                             // per query tile: [2 slabs][128 q][64 d]
-    unsigned char* p_s = q_s + TA_NQ * TA_QTILE;             // per query tile: [128 q][64 keys]
+    unsigned char* p_s = q_s + NQB * TA_QTILE;             // per query tile: [128 q][64 keys]
     unsigned char* kv_s = p_s + TA_NQ * TA_PTILE;            // per stage: K [2 slabs][64 keys][64 d], V the same
-    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + TA_STAGES * 2 * TA_KTILE);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + STAGES * 2 * TA_KTILE);
     // bars: [0] q_full, kv_full[S], kv_empty[S]; per query tile: s_full[2], s_free[2], p_ready, o_done
     uint64_t* kv_full = bars + 1;
-    uint64_t* kv_empty = kv_full + TA_STAGES;
-    uint64_t* s_full = kv_empty + TA_STAGES;                 // [qt][2]
+    uint64_t* kv_empty = kv_full + STAGES;
+    uint64_t* s_full = kv_empty + STAGES;                 // [qt][2]
     uint64_t* s_free = s_full + 2 * TA_NQ;                   // [qt][2]
     uint64_t* p_ready = s_free + 2 * TA_NQ;                  // [qt]
     uint64_t* o_done = p_ready + TA_NQ;                      // [qt]
@@ -166,17 +178,20 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // long tiles first (see attention_prefill_mma.cu)
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    // The head is the fastest grid index and the query tiles run from the last to the first: CTAs start in the
+    // order of their work (a causal tile's key range grows with its position), the longest of every head
+    // first, and the heads of a group walk the same keys at the same time.
+    const int tile = gridDim.y - 1 - blockIdx.y, h = blockIdx.x, b = blockIdx.z;
     const int slot = p.row_slot[b];
     const int q_len = slot >= 0 ? p.row_q_len[b] : 0;
-    if (tile * TA_ROWS >= q_len) return;                     // uniform for the CTA; nothing allocated yet
+    constexpr int CTA_ROWS = SPLIT ? TA_BM : TA_ROWS;        // query tokens of a CTA
+    if (tile * CTA_ROWS >= q_len) return;                    // uniform for the CTA; nothing allocated yet
     if ((ta_saddr(ta_raw) & 1023u) != 0) {                   // the swizzled tiles need a 1024-byte-aligned base
         if (threadIdx.x == 0) set_status(p.status, STATUS_WAIT_TIMEOUT);
         return;
     }
     const int ctx = p.row_ctx_len[b];
-    const int tok0 = p.row_q_start[b] + tile * TA_ROWS;      // first token of the CTA
+    const int tok0 = p.row_q_start[b] + tile * CTA_ROWS;     // first token of the CTA
     const int kvh = h / p.G;
     const int bs = p.block_size;
     // The CTA's two query tiles (128 rows each; the second may be empty) share every key tile.  Of the key
@@ -185,13 +200,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     int nq[TA_NQ], p_first[TA_NQ], q_lo[TA_NQ], q_hi[TA_NQ], it_lo[TA_NQ], it_hi[TA_NQ];
 #pragma unroll
     for (int qt = 0; qt < TA_NQ; ++qt) {
-        nq[qt] = max(0, min(TA_BM, q_len - tile * TA_ROWS - qt * TA_BM));
-        p_first[qt] = ctx + tile * TA_ROWS + qt * TA_BM;
+        const int first = tile * CTA_ROWS + (SPLIT ? 0 : qt * TA_BM);   // the group's first query in the step
+        nq[qt] = max(0, min(TA_BM, q_len - first));
+        p_first[qt] = ctx + first;
         q_hi[qt] = p_first[qt] + nq[qt];
         q_lo[qt] = p.window > 0 ? max(0, p_first[qt] - p.window + 1) : 0;
     }
     const int lo = q_lo[0];
-    const int hi = nq[1] > 0 ? q_hi[1] : q_hi[0];
+    const int hi = !SPLIT && nq[1] > 0 ? q_hi[1] : q_hi[0];
     const int t_begin = (lo / TA_BN) * TA_BN;
     const int n_tiles = (hi - t_begin + TA_BN - 1) / TA_BN;
 #pragma unroll
@@ -199,6 +215,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         it_lo[qt] = (q_lo[qt] / TA_BN * TA_BN - t_begin) / TA_BN;
         it_hi[qt] = nq[qt] > 0 ? (q_hi[qt] - t_begin + TA_BN - 1) / TA_BN : it_lo[qt];
     }
+    // whether group qt works on key tile `it`, and which of its own tiles (0, 1, ...) that is
+    auto mine = [&](int qt, int it, int& j) -> bool {
+        if (it < it_lo[qt] || it >= it_hi[qt]) return false;
+        j = it - it_lo[qt];
+        if (SPLIT) {
+            if ((j & 1) != qt) return false;
+            j >>= 1;
+        }
+        return true;
+    };
 
     if (threadIdx.x == 0) {
         abort_flag[0] = 0;
@@ -207,7 +233,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ta_saddr(bar)), "r"(count) : "memory");
         };
         init(&bars[0], 1);
-        for (int s = 0; s < TA_STAGES; ++s) { init(&kv_full[s], 1); init(&kv_empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { init(&kv_full[s], 1); init(&kv_empty[s], 1); }
         for (int i = 0; i < 2 * TA_NQ; ++i) { init(&s_full[i], 1); init(&s_free[i], 128); }   // s_free, p_ready: every softmax thread arrives
         for (int qt = 0; qt < TA_NQ; ++qt) { init(&p_ready[qt], 128); init(&o_done[qt], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -228,11 +254,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // next 32 copies together, one chunk ahead, so that no copy waits for a table entry ----
         if (lane == 0) {
             // rows beyond the last token of the step are zero-filled; rows of a following sequence are computed and dropped
-            ta_expect(ta_saddr(&bars[0]), TA_NQ * TA_QTILE);
+            ta_expect(ta_saddr(&bars[0]), NQB * TA_QTILE);
 #pragma unroll
-            for (int qt = 0; qt < TA_NQ; ++qt) {
-                ta_tma(ta_saddr(q_s + qt * TA_QTILE), &map_q, ta_saddr(&bars[0]), h * TA_D, tok0 + qt * TA_BM);
-                ta_tma(ta_saddr(q_s + qt * TA_QTILE + TA_QSLAB), &map_q, ta_saddr(&bars[0]), h * TA_D + 64, tok0 + qt * TA_BM);
+            for (int qt = 0; qt < NQB; ++qt) {
+                const int row = tok0 + qt * TA_BM;
+                ta_tma(ta_saddr(q_s + qt * TA_QTILE), &map_q, ta_saddr(&bars[0]), h * TA_D, row);
+                ta_tma(ta_saddr(q_s + qt * TA_QTILE + TA_QSLAB), &map_q, ta_saddr(&bars[0]), h * TA_D + 64, row);
             }
         }
         const int first_col = lo / bs;                        // blocks behind a window may have been given back
@@ -252,9 +279,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         int blk_cur = 0, blk_next = fetch(lane);
         int issued = 0;
         for (int it = 0; it < n_tiles; ++it) {
-            const int s = it % TA_STAGES;
+            const int s = it % STAGES;
             bool ok = true;
-            if (it >= TA_STAGES) ok = ta_wait(ta_saddr(&kv_empty[s]), ((it / TA_STAGES) - 1) & 1, abort_flag, p.status);
+            if (it >= STAGES) ok = ta_wait(ta_saddr(&kv_empty[s]), ((it / STAGES) - 1) & 1, abort_flag, p.status);
             if (!__all_sync(0xffffffffu, ok && *abort_flag == 0)) break;
             const uint32_t full = ta_saddr(&kv_full[s]);
             if (lane == 0) ta_expect(full, 2 * TA_KTILE);
@@ -279,8 +306,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         // giving up: the copies in flight must land before the CTA's shared memory is released
         if (lane == 0 && *abort_flag)
-            for (int it = max(0, issued - TA_STAGES); it < issued; ++it)
-                ta_wait(ta_saddr(&kv_full[it % TA_STAGES]), (it / TA_STAGES) & 1, abort_flag + 1, nullptr);
+            for (int it = max(0, issued - STAGES); it < issued; ++it)
+                ta_wait(ta_saddr(&kv_full[it % STAGES]), (it / STAGES) & 1, abort_flag + 1, nullptr);
     } else if (warp == 1 && lane == 0) {
         // ---- issuer of S = Q K^T ----
         // D float, A and B bf16, M 128, N = 64 keys, both operands K-major.  S of a query tile's j-th key tile
@@ -290,17 +317,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         bool ok = ta_wait(ta_saddr(&bars[0]), 0, abort_flag, p.status);
         for (int it = 0; ok && it < n_tiles; ++it) {
-            const int s = it % TA_STAGES;
-            ok = ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status);
+            const int s = it % STAGES;
+            ok = ta_wait(ta_saddr(&kv_full[s]), (it / STAGES) & 1, abort_flag, p.status);
             const uint32_t ks = ta_saddr(kv_s + s * 2 * TA_KTILE);
 #pragma unroll
             for (int qt = 0; qt < TA_NQ; ++qt) {
-                if (!ok || it < it_lo[qt] || it >= it_hi[qt]) continue;
-                const int j = it - it_lo[qt];
+                int j;
+                if (!ok || !mine(qt, it, j)) continue;
                 if (j >= 2) ok = ta_wait(ta_saddr(&s_free[qt * 2 + (j & 1)]), ((j >> 1) - 1) & 1, abort_flag, p.status);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t qa = ta_saddr(q_s + qt * TA_QTILE);
+                const uint32_t qa = ta_saddr(q_s + (SPLIT ? 0 : qt) * TA_QTILE);
 #pragma unroll
                 for (int kk = 0; kk < TA_D / 16; ++kk) {       // 8 steps over the head dimension
                     const uint32_t inner = (kk & 3) * 32;
@@ -317,14 +344,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(TA_D >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
             bool ok = true;
             for (int it = 0; ok && it < n_tiles; ++it) {
-                const int s = it % TA_STAGES;
+                const int s = it % STAGES;
                 // the tile's copies have landed (the other issuer saw it long ago; this thread must see it too)
-                ok = ta_wait(ta_saddr(&kv_full[s]), (it / TA_STAGES) & 1, abort_flag, p.status);
+                ok = ta_wait(ta_saddr(&kv_full[s]), (it / STAGES) & 1, abort_flag, p.status);
                 const uint32_t vs = ta_saddr(kv_s + s * 2 * TA_KTILE + TA_KTILE);
 #pragma unroll
                 for (int qt = 0; qt < TA_NQ; ++qt) {
-                    if (!ok || it < it_lo[qt] || it >= it_hi[qt]) continue;
-                    const int j = it - it_lo[qt];
+                    int j;
+                    if (!ok || !mine(qt, it, j)) continue;
                     ok = ta_wait(ta_saddr(&p_ready[qt]), j & 1, abort_flag, p.status);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -351,11 +378,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float scale_log2 = p.scale * 1.4426950408889634f;   // > 0: the maximum is taken over raw scores
         float m_run = -INFINITY, l_run = 0.f;                      // running maximum (raw score) and sum
         bool ok = true;
-        const int n_mine = it_hi[qt] - it_lo[qt];
+        const int n_both = it_hi[qt] - it_lo[qt];
+        const int n_mine = SPLIT ? (n_both + 1 - qt) >> 1 : n_both;
         unsigned char* my_p = p_s + qt * TA_PTILE;
         const uint32_t my_o = tmem_o + qt * TA_D;
         for (int j = 0; j < n_mine; ++j) {
-            const int it = it_lo[qt] + j;
+            const int it = it_lo[qt] + (SPLIT ? 2 * j + qt : j);
             const int t0 = t_begin + it * TA_BN;
             ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&s_full[qt * 2 + (j & 1)]), (j >> 1) & 1, abort_flag, p.status));
             if (!ok) break;
@@ -431,7 +459,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // zero them.  The tile has landed (S was computed from it).  Both query tiles do it (the same zeros),
             // each before its own P V is allowed to start.
             if (r < TA_BN && (t0 + r < lo || t0 + r >= hi)) {
-                unsigned char* vrow = kv_s + (it % TA_STAGES) * 2 * TA_KTILE + TA_KTILE + r * 128;
+                unsigned char* vrow = kv_s + (it % STAGES) * 2 * TA_KTILE + TA_KTILE + r * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     *reinterpret_cast<uint4*>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
@@ -445,22 +473,70 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         if (ok && n_mine > 0) ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (n_mine - 1) & 1, abort_flag, p.status));
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && n_mine > 0) {
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + ((size_t)(tok0 + qt * TA_BM + r) * p.n_q + h) * TA_D;
+        float w_own = l_run > 0.f ? 1.f / l_run : 0.f;          // what this thread's O is multiplied by
+        float w_other = 0.f;                                    // SPLIT: and the other group's
+        const float* o_other = nullptr;
+        bool writes = ok && n_mine > 0;
+        if (SPLIT) {
+            // Both groups are past their last product and every copy of the ring was consumed, once all 256
+            // threads have met: the ring is free, and takes the second group's O (float, [dim][row], so that
+            // a warp's rows are neighbours) with its maxima and sums behind it.
+            float* o_x = reinterpret_cast<float*>(kv_s);
+            float* m_x = o_x + TA_D * TA_BM;
+            float* l_x = m_x + TA_BM;
+            const bool has_other = (n_both >> 1) > 0;           // the second group had a key tile at all
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const bool fine = ok && *abort_flag == 0;
+            if (qt == 1 && fine && n_mine > 0) {
+                m_x[r] = m_run == -INFINITY ? -INFINITY : m_run * scale_log2;
+                l_x[r] = l_run;
+#pragma unroll 1
+                for (int c0 = 0; c0 < TA_D; c0 += 32) {
+                    uint32_t v[32];
+                    ta_ld32(my_o + lane_base + c0, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o_x[(c0 + c) * TA_BM + r] = __uint_as_float(v[c]);
+                }
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            writes = qt == 0 && fine && n_mine > 0;
+            if (writes) {
+                const float m0 = m_run == -INFINITY ? -INFINITY : m_run * scale_log2;
+                const float m1 = has_other ? m_x[r] : -INFINITY;
+                const float l1 = has_other ? l_x[r] : 0.f;
+                const float m = fmaxf(m0, m1);
+                const float a0 = m0 == -INFINITY ? 0.f : ta_ex2(m0 - m);
+                const float a1 = m1 == -INFINITY ? 0.f : ta_ex2(m1 - m);
+                const float l = l_run * a0 + l1 * a1;
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                w_own = a0 * inv;
+                w_other = a1 * inv;
+                if (has_other) o_other = o_x + r;
+            }
+        }
+        if (writes) {
+            __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.out) + ((size_t)(tok0 + (SPLIT ? 0 : qt * TA_BM) + r) * p.n_q + h) * TA_D;
 #pragma unroll 1
             for (int c0 = 0; c0 < TA_D; c0 += 32) {
                 uint32_t v[32];
                 ta_ld32(my_o + lane_base + c0, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (SPLIT && o_other != nullptr) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        v[c] = __float_as_uint(fmaf(o_other[(c0 + c) * TA_BM], w_other, __uint_as_float(v[c]) * w_own));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * w_own);
+                }
                 if (r < nq[qt]) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * e]) * inv,
-                                                                            __uint_as_float(v[c + 2 * e + 1]) * inv);
+                            const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * e]), __uint_as_float(v[c + 2 * e + 1]));
                             w[e] = *reinterpret_cast<const uint32_t*>(&pk);
                         }
                         *reinterpret_cast<uint4*>(orow + c0 + c) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -521,13 +597,25 @@ static int ta_map(const void* ptr, long long rows, int cols, int box_rows, CUten
     return 0;
 }
 
+static int g_ta_form = 0;
+
+static int ta_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
 // Returns 1 when it does not take the sizes (the caller falls back to the mma.sync kernel):
 // head size 128, block size a multiple of 8 that divides 128, no split of the keys.
 int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_q_len, cudaStream_t stream) {
     if (p.d != TA_D || p.n_splits != 1) return 1;
     const int bs = p.block_size;
     if (bs < 8 || bs > 128 || bs % 8 != 0 || 128 % bs != 0) return 1;
-    if (p.n_q > 65535 || n_rows > 65535) return 1;
+    if ((max_q_len + TA_BM - 1) / TA_BM > 65535 || n_rows > 65535) return 1;
     CUtensorMap mq, mk, mv;
     if (ta_map(p.q, T, p.n_q * TA_D, TA_BM, &mq) != 0) return 1;
     const long long pool_rows = (long long)p.num_blocks * p.n_kv * bs;
@@ -536,15 +624,28 @@ int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_
     if (ta_map(p.v_pool, pool_rows, TA_D, box, &mv) != 0) return 1;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TA_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TA_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TA_SMEM);
         if (e != cudaSuccess) return fail(-3, "attention: cannot get %d bytes of shared memory: %s", TA_SMEM, cudaGetErrorString(e));
         configured = true;
     }
-    const int q_tiles = (max_q_len + TA_ROWS - 1) / TA_ROWS;
-    dim3 grid(q_tiles, p.n_q, n_rows);
-    attn_prefill_tcgen05_kernel<<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p);
+    // Two query tiles per CTA share every key tile; while that leaves SMs without a CTA, one query tile per
+    // CTA with its key tiles dealt to the two softmax groups finishes sooner.
+    const int shared_ctas = ((max_q_len + TA_ROWS - 1) / TA_ROWS) * p.n_q * n_rows;
+    const bool split = g_ta_form == 2 || (g_ta_form == 0 && shared_ctas < ta_sm_count());
+    if (split) {
+        dim3 grid(p.n_q, (max_q_len + TA_BM - 1) / TA_BM, n_rows);
+        attn_prefill_tcgen05_kernel<true><<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p);
+    } else {
+        dim3 grid(p.n_q, (max_q_len + TA_ROWS - 1) / TA_ROWS, n_rows);
+        attn_prefill_tcgen05_kernel<false><<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p);
+    }
     return check_launch("attention_prefill_tcgen05");
 }
 
 }  // namespace fd
+
+// 0: the launcher chooses; 1: two query tiles per CTA; 2: one query tile, its key tiles dealt to the two groups
+extern "C" void fd_attn_prefill_set_form(int form) { fd::g_ta_form = form; }
 

@@ -18,7 +18,7 @@ from typing import Dict, Iterator, List, Optional, Sequence, Tuple, Union
 import torch
 
 from .. import kernels as K
-from ..cache.paged import PagedCache
+from ..cache.paged import DEFAULT_BLOCK_SIZE, PagedCache
 from ..config import load_config
 from ..sampling.sampler import Sampler
 from ..weights import loader as W
@@ -53,14 +53,14 @@ class Engine(Backend):
         self._graph_decoder: Optional[GraphDecoder] = None
 
     # -- caches -----------------------------------------------------------
-    def new_paged_cache(self, batch_size: int, max_len: int, block_size: int = 16,
+    def new_paged_cache(self, batch_size: int, max_len: int, block_size: int = DEFAULT_BLOCK_SIZE,
                         slack_blocks: int = 8) -> PagedCache:
         """A cache for ``batch_size`` sequences of up to ``max_len`` tokens
         (engine/model.py:115-135 of the reference, same arguments)."""
         return self.model.new_cache(batch_size=batch_size, max_len=max_len, block_size=block_size,
                                     slack_blocks=slack_blocks)
 
-    def new_cache(self, max_tokens: int, block_size: int = 16, **kw) -> PagedCache:
+    def new_cache(self, max_tokens: int, block_size: int = DEFAULT_BLOCK_SIZE, **kw) -> PagedCache:
         return self.model.new_cache(max_tokens, block_size=block_size, **kw)
 
     # -- Backend of the generation loop -------------------------------------
@@ -120,7 +120,7 @@ class Engine(Backend):
 
     def generate(self, input_ids, max_new_tokens, cache: Optional[PagedCache] = None, *,
                  temperature=0.0, seed: int = 0, stop_token_ids: Optional[Sequence[int]] = None,
-                 max_batch: Optional[int] = None, block_size: int = 16):
+                 max_batch: Optional[int] = None, block_size: int = DEFAULT_BLOCK_SIZE):
         """Generate up to ``max_new_tokens`` tokens for every prompt.
 
         ``input_ids``: a [B, S] tensor (the reference's form; returns a
@@ -142,7 +142,7 @@ class Engine(Backend):
 
     def stream(self, input_ids, max_new_tokens, cache: Optional[PagedCache] = None, *, temperature=0.0,
                seed: int = 0, stop_token_ids: Optional[Sequence[int]] = None, max_batch: Optional[int] = None,
-               block_size: int = 16) -> Iterator[List[Tuple[int, int, Optional[str]]]]:
+               block_size: int = DEFAULT_BLOCK_SIZE) -> Iterator[List[Tuple[int, int, Optional[str]]]]:
         """Like ``generate`` but yields, step by step, the new token of every
         live sequence as host integers: (prompt index, token, finish reason)."""
         requests = self._requests(input_ids, max_new_tokens, temperature, stop_token_ids)

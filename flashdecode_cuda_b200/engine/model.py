@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from .. import kernels as K
-from ..cache.paged import KVGroupSpec, PagedCache, StateSpec
+from ..cache.paged import DEFAULT_BLOCK_SIZE, KVGroupSpec, PagedCache, StateSpec
 from ..parts.base import KVRequest, LayerCache, Runtime
 from ..registry import architecture, part_class
 from ..weights import loader as W
@@ -261,7 +261,7 @@ class Model:
         return list(self._layout[0])
 
     def new_cache(self, max_tokens: Optional[int] = None, *, batch_size: Optional[int] = None,
-                  max_len: Optional[int] = None, block_size: int = 16, max_slots: Optional[int] = None,
+                  max_len: Optional[int] = None, block_size: int = DEFAULT_BLOCK_SIZE, max_slots: Optional[int] = None,
                   slack_blocks: int = 0) -> PagedCache:
         """A cache sized either by ``max_tokens`` (the most tokens that live
         sequences hold at any time, each sequence rounded up to a multiple of

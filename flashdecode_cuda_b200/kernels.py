@@ -82,6 +82,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemm_tc_supported": [I, I, I],
         "fd_gemm_tc_set_wide": [I],
+        "fd_attn_prefill_set_form": [I],
         "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
         "fd_gemm_tc_qkv_rope": [P, P, P, I, P, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemv_splits": [I, I, I, I, I],
@@ -255,6 +256,15 @@ def gemm_tc_set_wide(on) -> None:
     256 x 256 tile (``tcgen05.mma.cta_group::2``), 1 / True = one persistent CTA per SM with 128 x 256
     tiles, 0 / False = 128 x 128 tiles, one per CTA, everywhere.  For tests and measurements."""
     lib().fd_gemm_tc_set_wide(int(on))
+
+
+def attn_prefill_set_form(form: int) -> None:
+    """Which form the tcgen05 prompt attention takes from now on: 1 = a CTA takes 256 queries as two query
+    tiles that share every key tile; 2 = a CTA takes 128 queries and deals their key tiles to its two groups
+    of softmax warps, which add up their results at the end (half the chain of key tiles per query tile:
+    for prompts too short to fill the GPU); 0 = the launcher chooses by the number of CTAs.  For tests and
+    measurements."""
+    lib().fd_attn_prefill_set_form(int(form))
 
 
 def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,

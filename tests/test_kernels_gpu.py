@@ -606,10 +606,23 @@ def test_attention_decode_tensor_cores(n_q, n_kv, d, bs, n_splits, split_len):
 
 
 # head size 128: K.attention takes the tcgen05 kernel, K.attention_mma_sync the mma.sync one
-PROMPT_KERNELS = [K.attention, K.attention_mma_sync]
+def _attention_in_form(form):
+    def fn(*args, **kwargs):
+        K.attn_prefill_set_form(form)
+        try:
+            return K.attention(*args, **kwargs)
+        finally:
+            K.attn_prefill_set_form(0)
+    return fn
 
 
-@pytest.mark.parametrize("fn", PROMPT_KERNELS, ids=["auto", "mma_sync"])
+# the dispatcher's own choice; the tcgen05 kernel with two query tiles per CTA; the same with one query tile whose
+# key tiles are dealt to the two softmax groups; the mma.sync kernel
+PROMPT_KERNELS = [K.attention, _attention_in_form(1), _attention_in_form(2), K.attention_mma_sync]
+PROMPT_IDS = ["auto", "two_tiles", "dealt_keys", "mma_sync"]
+
+
+@pytest.mark.parametrize("fn", PROMPT_KERNELS, ids=PROMPT_IDS)
 @pytest.mark.parametrize("n_q,n_kv,d,bs", [(12, 2, 128, 16), (7, 1, 128, 4), (5, 5, 64, 32), (6, 2, 64, 16), (28, 4, 128, 8)])
 def test_attention_prompts_tensor_cores(n_q, n_kv, d, bs, fn):
     """The dispatcher's tensor-core kernels for bfloat16 prompt steps: unequal
@@ -619,7 +632,7 @@ def test_attention_prompts_tensor_cores(n_q, n_kv, d, bs, fn):
     assert rel(got, want) < TOL["bfloat16"]
 
 
-@pytest.mark.parametrize("fn", PROMPT_KERNELS, ids=["auto", "mma_sync"])
+@pytest.mark.parametrize("fn", PROMPT_KERNELS, ids=PROMPT_IDS)
 @pytest.mark.parametrize("window", [1, 5, 63, 64, 65, 200])
 def test_attention_prompts_tensor_cores_window_and_far_key(window, fn):
     got, want, _ = run_attention("bfloat16", 6, 2, 64, 16, ctx=[0, 90, 7], new=[150, 70, 1], window=window, fn=fn)
@@ -634,23 +647,25 @@ def test_attention_prompts_tensor_cores_window_and_far_key(window, fn):
             assert rel(got, want) < TOL["bfloat16"], key_pos
 
 
-def test_attention_prompts_tcgen05_large_scores():
+@pytest.mark.parametrize("form", [1, 2], ids=["two_tiles", "dealt_keys"])
+def test_attention_prompts_tcgen05_large_scores(form):
     """The tcgen05 kernel moves a row's running maximum only when it grows by more than 2^8:
     scores that rise steadily along the keys (each tile a little above the last), scores that
     jump far, and a long prompt over several hundred keys must all come out the same."""
     for qk_scale, ramp in ((1.0, 0.0), (6.0, 0.0), (30.0, 0.0), (1.0, 0.05), (1.0, 0.125), (1.0, 1.0), (0.0, 0.03)):
-        got, want, _ = run_attention("bfloat16", 4, 2, 128, 16, ctx=[0, 300], new=[520, 200], fn=K.attention,
+        got, want, _ = run_attention("bfloat16", 4, 2, 128, 16, ctx=[0, 300], new=[520, 200], fn=_attention_in_form(form),
                                      qk_scale=qk_scale, ramp=ramp)
         assert rel(got, want) < TOL["bfloat16"], (qk_scale, ramp)
 
 
 @pytest.mark.parametrize("window", [1, 40, 127, 128, 129, 300])
 @pytest.mark.parametrize("bs", [8, 16, 64, 128])
-def test_attention_prompts_tcgen05_window(window, bs):
+@pytest.mark.parametrize("form", [1, 2], ids=["two_tiles", "dealt_keys"])
+def test_attention_prompts_tcgen05_window(window, bs, form):
     """Head size 128 goes to the tcgen05 kernel: windows around its tiles of 64 keys and 128
     queries, every block size it takes, prompts that continue a cached prefix."""
     got, want, _ = run_attention("bfloat16", 6, 2, 128, bs, ctx=[0, 150, 7, 256], new=[260, 130, 1, 128], window=window,
-                                 fn=K.attention)
+                                 fn=_attention_in_form(form))
     assert rel(got, want) < TOL["bfloat16"]
 
 
@@ -715,8 +730,8 @@ def test_sample_temperature_follows_the_distribution():
 # ---------------------------------------------------------------------------
 def test_attention_prompts_drawn_shapes():
     """Prompt steps at head size 128 with drawn group sizes, block sizes, cached prefixes, prompt lengths
-    around the 128- and 256-row tiles and windows (the tcgen05 kernel, and the decode kernel where every
-    sequence brings one token)."""
+    around the 128- and 256-row tiles and windows (both forms of the tcgen05 kernel in turn, and the decode
+    kernel where every sequence brings one token)."""
     import random
     rnd = random.Random(11)
     for case in range(40):
@@ -727,9 +742,10 @@ def test_attention_prompts_drawn_shapes():
         ctx = [rnd.choice([0, 0, rnd.randint(1, 300)]) for _ in range(n_seq)]
         new = [rnd.choice([1, rnd.randint(2, 127), 128, 129, 255, 256, 257, rnd.randint(130, 600)]) for _ in range(n_seq)]
         window = rnd.choice([0, 0, 1, rnd.randint(2, 700), 64, 128, 256])
-        got, want, _ = run_attention("bfloat16", n_q, n_kv, 128, bs, ctx=ctx, new=new, window=window, fn=K.attention,
-                                     seed=case)
-        assert rel(got, want) < TOL["bfloat16"], dict(n_q=n_q, n_kv=n_kv, bs=bs, ctx=ctx, new=new, window=window)
+        got, want, _ = run_attention("bfloat16", n_q, n_kv, 128, bs, ctx=ctx, new=new, window=window,
+                                     fn=_attention_in_form(1 + case % 2), seed=case)
+        assert rel(got, want) < TOL["bfloat16"], dict(n_q=n_q, n_kv=n_kv, bs=bs, ctx=ctx, new=new, window=window,
+                                                      form=1 + case % 2)
 
 
 def test_attention_decode_drawn_shapes():
