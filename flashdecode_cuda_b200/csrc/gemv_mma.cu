@@ -86,14 +86,36 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
             }
         }
     }
-    for (; kc < n_chunks; kc += WK) {
-        const uint4 a = ldg_stream(w0 + kc * 32);
-        const uint4 b = ldg_stream(w1 + kc * 32);
+    // The rest of the range (fewer than UNROLL chunks for this warp) in groups of REST chunks, again with every
+    // load of a group issued before the first is used: one chunk at a time, each waiting for its own load, cost
+    // a trip to memory per chunk - for K = 1536 and 16 warps slicing K that was all three of a warp's chunks.
+    // A group's places beyond the range read the range's last chunk once more (it is in L2) against zeros for x.
+    constexpr int REST = NT > 1 ? 2 : (UNROLL > 4 ? 4 : (UNROLL > 1 ? UNROLL - 1 : 1));     // NT 2 with groups of 4: 78 registers, a CTA less per SM
+    for (; kc < n_chunks; kc += REST * WK) {
+        uint4 a[REST], b[REST], xv[REST][NT];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const uint4 xv = __ldg(reinterpret_cast<const uint4*>(xb[nt] + kc * 32));
-            mma16816(acc[nt], a.x, b.x, a.y, b.y, xv.x, xv.y);
-            mma16816(acc[nt], a.z, b.z, a.w, b.w, xv.z, xv.w);
+        for (int u = 0; u < REST; ++u) {
+            const int c = min(kc + u * WK, n_chunks - 1);
+            a[u] = ldg_stream(w0 + c * 32);
+            b[u] = ldg_stream(w1 + c * 32);
+        }
+#pragma unroll
+        for (int u = 0; u < REST; ++u) {
+            const bool in = kc + u * WK < n_chunks;            // the same for all lanes of the warp
+            const int c = min(kc + u * WK, n_chunks - 1);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                xv[u][nt] = __ldg(reinterpret_cast<const uint4*>(xb[nt] + c * 32));
+                if (!in) xv[u][nt] = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < REST; ++u) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                mma16816(acc[nt], a[u].x, b[u].x, a[u].y, b[u].y, xv[u][nt].x, xv[u][nt].y);
+                mma16816(acc[nt], a[u].z, b[u].z, a[u].w, b[u].w, xv[u][nt].z, xv[u][nt].w);
+            }
         }
     }
 
