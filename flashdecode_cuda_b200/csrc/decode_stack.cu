@@ -249,7 +249,16 @@ __device__ __forceinline__ void ds_gemv(const GemvJob& jb, const RopeArgs& ra, f
                 }
             }
         }
-        if (wk == 0 && tile < tiles) gemv_epilogue<NT>(gp, ra, acc, row0, split, r, q);
+        if (wk == 0 && tile < tiles) {
+            RopePre<NT> pre;
+            if (gp.mode == 4) {
+                rope_prefetch_first<NT>(gp, ra, q, pre);
+                rope_prefetch_rest<NT>(gp, ra, row0, r, pre);
+                gemv_epilogue<NT, true>(gp, ra, acc, row0, split, r, q, pre);
+            } else {
+                gemv_epilogue<NT, false>(gp, ra, acc, row0, split, r, q, pre);
+            }
+        }
         if (WK > 1) __syncthreads();                            // the sums have been read: the next item may write
     }
 }

@@ -52,13 +52,58 @@ struct RopeArgs {
     int n_q, n_kv, d, write_kv;
 };
 
+// Mode 4: what a thread's epilogue needs from the step's index arrays and tables, per x row it holds
+// (m = nt * 8 + q * 2 + e at index nt * 2 + e).  Every value hangs on a chain of loads (token -> sequence ->
+// slot -> block; position -> cosine and sine): three trips to L2 one after another, which in the epilogue were
+// most of its time.  They are fetched in two steps instead: the token's sequence and position before the
+// product's first weight loads are issued (nothing waits for them there), the rest right after those loads are
+// issued, so that the chain's waits pass while the weights are on their way.
+template <int NT>
+struct RopePre {
+    int slot[NT * 2], pos[NT * 2], blk[NT * 2];      // slot: first the token's row of the step, then its slot
+    float c[NT * 2], sn[NT * 2];
+};
+
+template <int NT>
+__device__ __forceinline__ void rope_prefetch_first(const GemvParams& p, const RopeArgs& ra, int q, RopePre<NT>& pre) {
+#pragma unroll
+    for (int i = 0; i < NT * 2; ++i) {
+        const int m = (i >> 1) * 8 + q * 2 + (i & 1);
+        pre.slot[i] = m < p.M ? ra.tok_row[m] : -1;
+        pre.pos[i] = m < p.M ? ra.tok_pos[m] : 0;
+    }
+}
+
+template <int NT>
+__device__ __forceinline__ void rope_prefetch_rest(const GemvParams& p, const RopeArgs& ra, int row0, int r, RopePre<NT>& pre) {
+    const int d = ra.d, half = d >> 1, tiles_per_head = d >> 4;
+    const int tile = row0 >> 4;
+    const int head = tile / tiles_per_head, t_in = tile - head * tiles_per_head;
+    const bool is_v = head >= ra.n_q + ra.n_kv;
+    const int j0 = is_v ? t_in * 16 + r : t_in * 8 + r;
+    const bool live = head < ra.n_q + 2 * ra.n_kv;
+#pragma unroll
+    for (int i = 0; i < NT * 2; ++i) pre.slot[i] = live && pre.slot[i] >= 0 ? ra.row_slot[pre.slot[i]] : -1;
+#pragma unroll
+    for (int i = 0; i < NT * 2; ++i) {
+        pre.blk[i] = -1; pre.c[i] = 1.f; pre.sn[i] = 0.f;
+        const int slot = pre.slot[i], pos = pre.pos[i];
+        if (slot < 0 || pos < 0 || pos >= ra.table_len) continue;
+        if (!is_v) {
+            pre.c[i] = ra.cos_t[(size_t)pos * half + j0];
+            pre.sn[i] = ra.sin_t[(size_t)pos * half + j0];
+        }
+        if (head >= ra.n_q && ra.write_kv) pre.blk[i] = ra.block_table[(size_t)slot * ra.max_blocks + pos / ra.block_size];
+    }
+}
+
 // What the owner of a finished row tile does with it.  acc[nt][0..1]: W row row0, x rows
 // nt*8 + q*2 + {0,1}; acc[nt][2..3]: W row row0 + 8 (r = lane / 4, q = lane % 4, row0 the
 // tile's first row + r).
-template <int NT>
+template <int NT, bool ROPE>
 __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const RopeArgs& ra, float (&acc)[NT][4], int row0,
-                                              int split, int r, int q) {
-    if (p.mode == 4) {
+                                              int split, int r, int q, const RopePre<NT>& pre) {
+    if (ROPE) {                                               // mode 4
         const int d = ra.d, half = d >> 1, tiles_per_head = d >> 4;
         const int tile = row0 >> 4;
         const int head = tile / tiles_per_head, t_in = tile - head * tiles_per_head;
@@ -76,16 +121,15 @@ __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const RopeArg
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const int m = nt * 8 + q * 2 + e;
+                const int m = nt * 8 + q * 2 + e, i = nt * 2 + e;
                 if (m >= p.M) continue;
-                const int slot = ra.row_slot[ra.tok_row[m]];
-                if (slot < 0) continue;                       // padding row
+                if (pre.slot[i] < 0) continue;                // padding row
                 float v0 = acc[nt][e] + b0, v1 = acc[nt][2 + e] + b1;
-                int pos = ra.tok_pos[m];
+                const int pos = pre.pos[i];
                 const bool pos_ok = pos >= 0 && pos < ra.table_len;
-                if (!pos_ok) { set_status(ra.status, STATUS_BAD_POSITION); pos = 0; }
+                if (!pos_ok) set_status(ra.status, STATUS_BAD_POSITION);     // rotated by position 0's angle (0)
                 if (!is_v) {
-                    const float c = ra.cos_t[(size_t)pos * half + j0], sn = ra.sin_t[(size_t)pos * half + j0];
+                    const float c = pre.c[i], sn = pre.sn[i];
                     const float y0 = v0 * c - v1 * sn, y1 = v1 * c + v0 * sn;
                     v0 = y0; v1 = y1;
                 }
@@ -94,7 +138,7 @@ __device__ __forceinline__ void gemv_epilogue(const GemvParams& p, const RopeArg
                     o[j0] = __float2bfloat16_rn(v0);
                     o[j1] = __float2bfloat16_rn(v1);
                 } else if (ra.write_kv && pos_ok) {
-                    const int blk = ra.block_table[(size_t)slot * ra.max_blocks + pos / ra.block_size];
+                    const int blk = pre.blk[i];
                     if (blk < 0 || blk >= ra.num_blocks) { set_status(ra.status, STATUS_BAD_BLOCK); continue; }
                     const int kvh = is_v ? head - ra.n_q - ra.n_kv : head - ra.n_q;
                     __nv_bfloat16* pool = is_v ? ra.v_pool : ra.k_pool;

@@ -34,8 +34,10 @@ namespace fd {
 constexpr int GV_WARPS = 8;
 constexpr int GV_THREADS = GV_WARPS * 32;
 
-template <int NT, int WK, int UNROLL, bool CLUSTER, int W>
-__global__ void __launch_bounds__(W * 32)
+// ROPE: the instantiation for mode 4, which keeps its epilogue's inputs in registers across the main loop
+// (the other modes must not pay for those registers with a CTA less per SM).
+template <int NT, int WK, int UNROLL, bool CLUSTER, int W, bool ROPE>
+__global__ void __launch_bounds__(W * 32, (!ROPE && W == 8 && NT == 2) ? 4 : 0)     // 16 rows of x: four 8-warp CTAs per SM (at most 64 registers)
 gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
     constexpr int WR = W / WK;
     __shared__ float red[WK > 1 ? W * 32 * NT * 4 : 1];
@@ -64,6 +66,9 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
     // neighbouring 64-byte pieces of the same rows
     pdl_launch_dependents();
     pdl_wait();
+    RopePre<NT> pre;
+    if (ROPE && wk == 0) rope_prefetch_first<NT>(p, ra, q, pre);
+    bool pre_done = !ROPE || wk != 0;       // the rest of the epilogue's inputs: once, behind the first weight loads
     int kc = wk;
     for (; kc + (UNROLL - 1) * WK < n_chunks; kc += UNROLL * WK) {
         uint4 a[UNROLL], b[UNROLL], xv[UNROLL][NT];
@@ -77,6 +82,7 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
                 xv[u][nt] = __ldg(reinterpret_cast<const uint4*>(xb[nt] + (kc + u * WK) * 32));
+        if (!pre_done) { rope_prefetch_rest<NT>(p, ra, row0, r, pre); pre_done = true; }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
@@ -109,6 +115,7 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
                 if (!in) xv[u][nt] = make_uint4(0u, 0u, 0u, 0u);
             }
         }
+        if (!pre_done) { rope_prefetch_rest<NT>(p, ra, row0, r, pre); pre_done = true; }
 #pragma unroll
         for (int u = 0; u < REST; ++u) {
 #pragma unroll
@@ -119,6 +126,7 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
         }
     }
 
+    if (!pre_done) rope_prefetch_rest<NT>(p, ra, row0, r, pre);       // a warp without a chunk of its own
     if (WK > 1) {
         // add the K slices of a row tile in the order wk = 0, 1, ...
         float* mine = red + (warp * 32 + lane) * NT * 4;
@@ -166,17 +174,25 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
     }
     if (WK > 1 && wk != 0) return;
 
-    gemv_epilogue<NT>(p, ra, acc, row0, split, r, q);
+    gemv_epilogue<NT, ROPE>(p, ra, acc, row0, split, r, q, pre);
 }
 
 template <int NT, int WK, int UNROLL, int W = GV_WARPS>
 static int launch_gemv(const GemvParams& p, const RopeArgs& ra, cudaStream_t stream) {
     constexpr int rows = 16 * (W / WK);
     dim3 grid((p.N + rows - 1) / rows, p.n_splits);
+    if (p.mode == 4) {
+        if (p.n_splits > 1)
+            return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, true, W, true>, grid, dim3(W * 32), 0, stream,
+                          dim3(1, p.n_splits, 1), p, ra);
+        return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, false, W, true>, grid, dim3(W * 32), 0, stream,
+                      dim3(1, 1, 1), p, ra);
+    }
     if (p.n_splits > 1 && p.mode != 0)
-        return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, true, W>, grid, dim3(W * 32), 0, stream,
+        return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, true, W, false>, grid, dim3(W * 32), 0, stream,
                       dim3(1, p.n_splits, 1), p, ra);
-    return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, false, W>, grid, dim3(W * 32), 0, stream, dim3(1, 1, 1), p, ra);
+    return launch("gemv_mma", gemv_mma_kernel<NT, WK, UNROLL, false, W, false>, grid, dim3(W * 32), 0, stream,
+                  dim3(1, 1, 1), p, ra);
 }
 
 // Measured on B200 (graph-timed, weights beyond L2): wide matrices stream best with 32 rows
