@@ -25,11 +25,17 @@
 // Keys and values come straight from the paged pools by TMA: one 2-D box of
 // (block_size keys x 64 dims) per cache block and half head, placed so that a
 // tile of 64 keys forms the canonical swizzled layout; three tiles are in
-// flight.  Roles: warp 0 issues TMA (the copies of a tile from as many lanes at
+// flight (four in the short-prompt form below).  Roles: warp 0 issues TMA (the copies of a tile from as many lanes at
 // once, the block numbers fetched 32 at a time ahead of use), warp 1 issues
 // Q K^T and owns the tensor-memory allocation, warps 2-9 do the softmax and the
 // epilogue, warp 10 issues P V.  Every mbarrier wait is bounded in time; a wait
 // that runs out sets a status bit and the CTA winds down (see gemm_tcgen05.cu).
+//
+// CTAs start in the order of their work: the head is the grid's fastest index
+// and the query tiles run from the last (most keys) to the first, over all
+// heads, so no long tile starts in a late wave.  A prompt so short that this
+// grid leaves SMs empty runs a second form of the kernel (SPLIT below): 128
+// queries per CTA, their key tiles dealt to the two groups of softmax warps.
 #include <cuda.h>
 #include <math.h>
 
