@@ -156,6 +156,7 @@ class PagedCache:
             s.name: torch.zeros((max_slots, *s.shape), dtype=s.dtype, device=self.device) for s in states}
         self.slot_alloc = IdAllocator(max_slots, "slot")
         self.slots = [SlotRecord() for _ in range(max_slots)]
+        self.lengths_version = 0        # grows whenever a slot's sequence or its length changes (admit, release, advance)
 
     # ------------------------------------------------------------------ slots
     def admit(self) -> int:
@@ -163,6 +164,7 @@ class PagedCache:
         (slot,) = self.slot_alloc.allocate(1)
         rec = self.slots[slot]
         rec.state, rec.length = ACTIVE, 0
+        self.lengths_version += 1
         rec.blocks = [[] for _ in self.groups]
         for st in self.states.values():
             st[slot].zero_()
@@ -179,6 +181,7 @@ class PagedCache:
                 if b >= 0:
                     g.set_entry(slot, col, -1)
         rec.state, rec.length, rec.blocks = FREE, 0, []
+        self.lengths_version += 1
         self.slot_alloc.free([slot])
 
     def _record(self, slot: int) -> SlotRecord:
@@ -230,6 +233,7 @@ class PagedCache:
         if self.blocks_needed(rec.length + n) > min((len(b) for b in rec.blocks), default=1 << 30):
             raise ValueError(f"slot {slot}: advancing by {n} beyond the reserved blocks")
         rec.length += n
+        self.lengths_version += 1
         for gi, g in enumerate(self.groups):
             w = g.spec.window
             if w is None:

@@ -64,7 +64,9 @@ class GraphDecoder:
         self.last_n = 0
         self.launches_per_step = 0
         self._host_out: Optional[torch.Tensor] = None
-        self._ahead: Optional[Tuple] = None          # (graph, slots) whose next lengths are in the graph's index array already
+        # (graph, slots, the cache's lengths_version): the next step's slots and lengths are in that graph's index
+        # array already; void as soon as any sequence of the cache has started, ended or grown since
+        self._ahead: Optional[Tuple] = None
 
     # ------------------------------------------------------------------
     def _key(self, n: int, longest: int, greedy: bool, seed: int) -> Tuple:
@@ -92,8 +94,8 @@ class GraphDecoder:
         h = g.host
         h[0:n] = tokens
         ahead, self._ahead = self._ahead, None
-        if ahead is None or ahead[0] is not g or ahead[1] != tuple(slots):
-            self._fill_lengths(g, B, slots)     # else: written while the GPU ran the step before
+        if ahead is None or ahead[0] is not g or ahead[1] != tuple(slots) or ahead[2] != self.cache.lengths_version:
+            self._fill_lengths(g, B, slots)     # else: written while the GPU ran the step before, and still true
         self.model._staging.upload(h, g.meta)
 
     def _fill_lengths(self, g: _Graph, B: int, slots: Sequence[int]) -> None:
@@ -186,7 +188,7 @@ class GraphDecoder:
             cache.sync()
             if g.host is not None and n == g.n_rows_real:
                 self._fill_lengths(g, key[0], slots)
-                self._ahead = (g, tuple(slots))
+                self._ahead = (g, tuple(slots), cache.lengths_version)
         except (ValueError, PoolExhausted):
             pass
         return g.sampled

@@ -93,6 +93,40 @@ def test_graph_replay_equals_eager_steps(folders):
     assert a == b
 
 
+def test_new_sequences_in_the_same_slots_of_the_same_graph(folders):
+    """The decoder fills in the next step's slots and lengths while a step runs.  When the
+    sequences end instead and new ones start in the same slots, in the same order, with the
+    same graph, what it filled in is stale and must not be used."""
+    from flashdecode_cuda_b200.engine.decode import GraphDecoder
+    eng = fd.load(folders["B"], device="cuda", dtype="float32")
+    raw, w = raw_config(folders["B"]), weights_of(folders["B"])
+    model = eng.model
+    cache = model.new_cache(max_tokens=256, block_size=8)
+    dec = GraphDecoder(model, cache)
+
+    def run(prompts, n_new):
+        slots = [cache.admit() for _ in prompts]
+        toks = eng.sampler.sample(model.step(cache, slots, prompts, "last")).tolist()
+        out = [[t] for t in toks]
+        for _ in range(n_new - 1):
+            dec.run(slots, toks)
+            toks = dec.read_tokens(len(slots))
+            for o, t in zip(out, toks):
+                o.append(t)
+        for s in reversed(slots):            # the allocator hands the last freed slot out first
+            cache.release(s)
+        return slots, out
+
+    first = prompts_for(raw["vocab_size"], [9, 4], seed=11)
+    second = prompts_for(raw["vocab_size"], [3, 17], seed=12)
+    slots_a, got_a = run(first, 6)
+    slots_b, got_b = run(second, 6)
+    assert slots_a == slots_b and len(dec.graphs) == 1      # the case this test is about
+    assert got_a == [P.generate(raw, w, p, 6) for p in first]
+    assert got_b == [P.generate(raw, w, p, 6) for p in second]
+    model.check_status()
+
+
 def test_command_line(folders, tmp_path):
     cmd = [sys.executable, "-m", "flashdecode_cuda_b200", "generate", "--model", str(folders["B"]),
            "--prompt-ids", "5,6,7", "--prompt-ids", "300,2", "--max-new-tokens", "5", "--dtype", "float32",
