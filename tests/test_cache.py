@@ -156,3 +156,27 @@ def test_random_traffic_keeps_the_invariants():
         c.release(s)
     c.check_invariants()
     assert c.blocks_in_use() == [0, 0] and c.slot_alloc.num_used == 0
+
+
+def test_lengths_version_moves_with_sequences_and_lengths_only():
+    """Whoever keeps something derived from the slots' lengths (the decoder's index array filled
+    ahead) compares this counter: it must move when a sequence starts, ends or grows, and must
+    not move when blocks are only reserved."""
+    c = make()
+    v0 = c.lengths_version
+    s = c.admit()
+    v1 = c.lengths_version
+    assert v1 != v0
+    c.reserve([(s, 6)])
+    c.sync()
+    assert c.lengths_version == v1
+    c.advance(s, 6)
+    v2 = c.lengths_version
+    assert v2 != v1
+    c.reserve([(s, 1)])                              # the decoder's reservation for a step that may not come
+    assert c.lengths_version == v2
+    c.release(s)
+    v3 = c.lengths_version
+    assert v3 != v2
+    assert c.admit() == s and c.lengths_version != v3     # the same slot with another sequence
+    c.check_invariants()
