@@ -21,13 +21,7 @@
 // Every wait on an mbarrier is bounded in time: if one runs out, the CTA sets
 // a bit in the status word, every role leaves its loop, tensor memory is freed
 // and the kernel returns (wrong output, a reported error, no hang).
-#include <cuda.h>
-
-#include <map>
-#include <mutex>
-#include <tuple>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace fd {
 
@@ -37,7 +31,6 @@ constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;          // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;          // 16 KB
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_SMEM = TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr unsigned long long TC_WAIT_NS = 200ull * 1000 * 1000;   // 0.2 s per wait, then give up
 
 struct TcParams {
     const void* bias;      // [N] or null
@@ -47,100 +40,9 @@ struct TcParams {
     int mode;              // 1: bf16 [M, N]; 2: float [M, N]; 3: gated, bf16 [M, N / 2];
                            // 4: q/k/v projection with rotary encoding and cache append (TcRope)
     int bias_f32;
+    unsigned long long wait_ns;   // limit of every bounded wait
+    int skip_last;                // tests only: the producer leaves out its very last copy, so that a wait runs out
 };
-
-// Mode 4: the rows of W (columns of the product) are the q heads, the k heads, then the v
-// heads; inside a q or k head they come in tiles of 16: dims 8t .. 8t+7, then their rotation
-// partners d/2 + 8t .. d/2 + 8t+7; v heads in natural order.  `out` is q_out [M, n_q d].
-struct TcRope {
-    const float* cos_t;          // [table_len, d/2]
-    const float* sin_t;
-    const int* tok_row;          // [M]
-    const int* tok_pos;          // [M]
-    const int* row_slot;
-    __nv_bfloat16* k_pool;       // [num_blocks, n_kv, block_size, d]
-    __nv_bfloat16* v_pool;
-    const int* block_table;
-    int table_len, max_blocks, num_blocks, block_size;
-    int n_q, n_kv, d, write_kv;
-};
-
-// ---- PTX wrappers ---------------------------------------------------------
-__device__ __forceinline__ uint32_t s_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait for the phase with the given parity.  False: the time ran out (or another
-// thread already gave up); the caller leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    unsigned long long t0 = 0;
-    for (uint32_t spins = 0;; ++spins) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((spins & 63) != 63) continue;                    // the clock and the flag only now and then
-        if (*abort_flag) return false;
-        if (t0 == 0) t0 = global_ns();
-        else if (global_ns() - t0 > TC_WAIT_NS) {
-            *abort_flag = 1;
-            set_status(status, STATUS_WAIT_TIMEOUT);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t v[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, laid out
-// by TMA with the 128-byte swizzle: 8-row groups of 1024 bytes (SBO), version 1, layout 2.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFF) >> 4);       // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                       // leading byte offset: not used by swizzled K-major layouts
-    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                       // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                       // 128-byte swizzle
-    return d;
-}
 
 // Mode 4: where the token of an output row lives in the cache.
 struct TcToken {
@@ -354,19 +256,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         for (int it = 0; it < k_iters; ++it) {
             const int s = it % TC_STAGES;
             if (it >= TC_STAGES &&
-                !mbar_wait(s_addr(&bars[TC_STAGES + s]), ((it / TC_STAGES) - 1) & 1, abort_flag, p.status)) break;
+                !mbar_wait(s_addr(&bars[TC_STAGES + s]), ((it / TC_STAGES) - 1) & 1, abort_flag, p.status, p.wait_ns)) break;
             if (*abort_flag) break;
             const uint32_t full = s_addr(&bars[s]);
             mbar_expect_tx(full, TC_STAGE_BYTES);
             unsigned char* a = tiles + s * TC_STAGE_BYTES;
             tma_load_2d(s_addr(a), &map_x, full, it * TC_BK, m0);
-            tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, full, it * TC_BK, n0);
+            if (!(p.skip_last && it == k_iters - 1)) tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, full, it * TC_BK, n0);
             issued = it + 1;
         }
         if (*abort_flag) {
             // let the copies already under way land before the CTA goes away
             for (int it = max(0, issued - TC_STAGES); it < issued; ++it)
-                mbar_wait(s_addr(&bars[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag + 1, nullptr);
+                mbar_wait(s_addr(&bars[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag + 1, nullptr, p.wait_ns);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
@@ -374,7 +276,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         for (int it = 0; it < k_iters; ++it) {
             const int s = it % TC_STAGES;
-            if (!mbar_wait(s_addr(&bars[s]), (it / TC_STAGES) & 1, abort_flag, p.status)) break;
+            if (!mbar_wait(s_addr(&bars[s]), (it / TC_STAGES) & 1, abort_flag, p.status, p.wait_ns)) break;
             tc_fence_after();
             const uint32_t a = s_addr(tiles + s * TC_STAGE_BYTES);
             const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
@@ -389,7 +291,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int quarter = warp & 3;
         const int m = m0 + quarter * 32 + lane;
         // all lanes of a warp must agree before the warp-wide tensor-memory loads
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&bars[2 * TC_STAGES]), 0, abort_flag, p.status));
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&bars[2 * TC_STAGES]), 0, abort_flag, p.status, p.wait_ns));
         tc_fence_after();
         const TcToken tk = tc_token(p, ra, m);
         if (ok) {
@@ -473,18 +375,19 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TW_BN;
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % TW_STAGES;
-                if (it >= TW_STAGES && !mbar_wait(s_addr(&empty[s]), ((it / TW_STAGES) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                if (it >= TW_STAGES && !mbar_wait(s_addr(&empty[s]), ((it / TW_STAGES) - 1) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
                 if (*abort_flag) { ok = false; break; }
                 const uint32_t fb = s_addr(&full[s]);
                 mbar_expect_tx(fb, TW_STAGE_BYTES);
                 unsigned char* a = tiles + s * TW_STAGE_BYTES;
                 tma_load_2d(s_addr(a), &map_x, fb, k * TC_BK, m0);
+                if (p.skip_last && k == k_iters - 1 && tile + (int)gridDim.x >= n_tiles) continue;       // tests: this CTA's very last copy
                 tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);     // 256 rows of W in one box
             }
         }
         if (*abort_flag) {
             for (int j = max(0, it - TW_STAGES); j < it; ++j)
-                mbar_wait(s_addr(&full[j % TW_STAGES]), (j / TW_STAGES) & 1, abort_flag + 1, nullptr);
+                mbar_wait(s_addr(&full[j % TW_STAGES]), (j / TW_STAGES) & 1, abort_flag + 1, nullptr, p.wait_ns);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
@@ -493,12 +396,12 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++t) {
             const int buf = t & 1;
-            if (t >= 2 && !mbar_wait(s_addr(&acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status)) break;
+            if (t >= 2 && !mbar_wait(s_addr(&acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status, p.wait_ns)) break;
             tc_fence_after();
             const uint32_t acc = tmem + buf * TW_BN;
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % TW_STAGES;
-                if (!mbar_wait(s_addr(&full[s]), (it / TW_STAGES) & 1, abort_flag, p.status)) { ok = false; break; }
+                if (!mbar_wait(s_addr(&full[s]), (it / TW_STAGES) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t a = s_addr(tiles + s * TW_STAGE_BYTES);
                 const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
@@ -521,7 +424,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TW_BN;
             const int m = m0 + quarter * 32 + lane;
             const TcToken tk = tc_token(p, ra, m);
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status)) &&
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, p.wait_ns)) &&
                             *abort_flag == 0;
             if (!__all_sync(0xffffffffu, ok)) break;
             tc_fence_after();
@@ -563,21 +466,6 @@ constexpr int TP_B_BYTES = 128 * TC_BK * 2;                   // this CTA's half
 constexpr int TP_STAGE_BYTES = TC_A_BYTES + TP_B_BYTES;       // 32 KB
 constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// the shared::cluster address of the same variable in the CTA of the given rank
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
@@ -593,10 +481,6 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uin
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
-}
-
 __global__ void __launch_bounds__(TW_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const TcParams p, const TcRope ra, const int tiles_m, const int tiles_n) {
@@ -650,12 +534,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const int n0 = (tile / tiles_m) * TW_BN + (int)rank * TC_BN;
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % TP_STAGES;
-                if (it >= TP_STAGES && !mbar_wait(s_addr(&empty[s]), ((it / TP_STAGES) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+                if (it >= TP_STAGES && !mbar_wait(s_addr(&empty[s]), ((it / TP_STAGES) - 1) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
                 if (*abort_flag) { ok = false; break; }
                 if (leader) mbar_expect_tx(s_addr(&full[s]), 2 * TP_STAGE_BYTES);
                 const uint32_t fb = map_to_rank(s_addr(&full[s]), 0);
                 unsigned char* a = tiles + s * TP_STAGE_BYTES;
                 tma_load_2d_pair(s_addr(a), &map_x, fb, k * TC_BK, m0);
+                if (p.skip_last && k == k_iters - 1 && tile + n_pairs >= n_tiles) continue;              // tests: this CTA's very last copy
                 tma_load_2d_pair(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);
             }
         }
@@ -664,7 +549,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         if (*abort_flag) {
             if (leader) {
                 for (int j = max(0, it - TP_STAGES); j < it; ++j)
-                    mbar_wait(s_addr(&full[j % TP_STAGES]), (j / TP_STAGES) & 1, abort_flag + 1, nullptr);
+                    mbar_wait(s_addr(&full[j % TP_STAGES]), (j / TP_STAGES) & 1, abort_flag + 1, nullptr, p.wait_ns);
             } else {
                 const unsigned long long t0 = global_ns();
                 while (global_ns() - t0 < 1000000ull) { }
@@ -677,12 +562,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         bool ok = true;
         for (int tile = pair; ok && tile < n_tiles; tile += n_pairs, ++t) {
             const int buf = t & 1;
-            if (t >= 2 && !mbar_wait(s_addr(&acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+            if (t >= 2 && !mbar_wait(s_addr(&acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
             tc_fence_after();
             const uint32_t acc = tmem + buf * TW_BN;
             for (int k = 0; k < k_iters; ++k, ++it) {
                 const int s = it % TP_STAGES;
-                if (!mbar_wait(s_addr(&full[s]), (it / TP_STAGES) & 1, abort_flag, p.status)) { ok = false; break; }
+                if (!mbar_wait(s_addr(&full[s]), (it / TP_STAGES) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t a = s_addr(tiles + s * TP_STAGE_BYTES);
                 const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
@@ -705,7 +590,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const int m0 = (tile % tiles_m) * (2 * TC_BM) + (int)rank * TC_BM, n0 = (tile / tiles_m) * TW_BN;
             const int m = m0 + quarter * 32 + lane;
             const TcToken tk = tc_token(p, ra, m);
-            const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status)) &&
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, p.wait_ns)) &&
                             *abort_flag == 0;
             if (!__all_sync(0xffffffffu, ok)) break;
             tc_fence_after();
@@ -731,51 +616,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 }
 
 // ---- host side ------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-    return fn;
-}
-
-// Tensor map of a row-major bf16 matrix [rows, cols] read in boxes of box_rows (128 or 256) rows x 64 columns
-// with the 128-byte swizzle.  Maps are cached by (address, shape): weights and workspace
-// buffers keep their addresses.
-static int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out, int box_rows = TC_BM) {
-    static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    auto key = std::make_tuple(ptr, rows, cols, box_rows);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return fail(-4, "gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUtensorMap m;
-    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(-4, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d for a %d x %d matrix", (int)r, rows, cols);
-    if (cache.size() > 4096) cache.clear();
-    cache[key] = m;
-    *out = m;
-    return 0;
-}
-
 int g_tc_wide = 1;      // 2: the two-SM kernel where N >= 256; 1: the wide one-SM kernel; 0: 128 x 128 tiles, one per CTA
 
 static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRope& ra, cudaStream_t stream,
@@ -795,7 +635,7 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM;
     const bool wide = g_tc_wide && p.N >= TW_BN;
     CUtensorMap mx, mw;
-    int rc = tensor_map(x, p.M, p.K, &mx);
+    int rc = tensor_map(x, p.M, p.K, &mx, TC_BM);
     if (rc != 0) return rc;
     const bool pair = wide && g_tc_wide == 2;
     rc = tensor_map(w, p.N, p.K, &mw, (wide && !pair) ? TW_BN : TC_BM);
@@ -851,6 +691,7 @@ extern "C" int fd_gemm_tc(const void* x, const void* w, const void* bias, int bi
                "gemm_tcgen05: x, W and out must be 16-byte aligned");
     TcParams p;
     p.bias = bias; p.out = out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = mode; p.bias_f32 = bias_f32;
+    p.wait_ns = g_tc_wait_ns; p.skip_last = g_tc_skip_last;
     TcRope ra = {};
     return launch_tc(x, w, p, ra, stream, "gemm_tcgen05");
 }
@@ -872,10 +713,20 @@ extern "C" int fd_gemm_tc_qkv_rope(const void* x, const void* w, const void* bia
                (uintptr_t)sin_t % 16 == 0 && (uintptr_t)bias % 16 == 0, -2, "gemm_tc_qkv_rope: all arrays must be 16-byte aligned");
     TcParams p;
     p.bias = bias; p.out = q_out; p.status = status; p.M = M; p.N = N; p.K = K; p.mode = 4; p.bias_f32 = bias_f32;
+    p.wait_ns = g_tc_wait_ns; p.skip_last = g_tc_skip_last;
     TcRope ra;
     ra.cos_t = cos_t; ra.sin_t = sin_t; ra.tok_row = tok_row; ra.tok_pos = tok_pos; ra.row_slot = row_slot;
     ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool; ra.block_table = block_table;
     ra.table_len = table_len; ra.max_blocks = max_blocks; ra.num_blocks = num_blocks; ra.block_size = block_size;
     ra.n_q = n_q; ra.n_kv = n_kv; ra.d = d; ra.write_kv = write_kv;
     return launch_tc(x, w, p, ra, stream, "gemm_tc_qkv_rope");
+}
+
+// Tests only: the limit of every bounded wait in the TMA + tcgen05 kernels (nanoseconds; 0 restores the
+// default of 0.2 s), and whether their TMA producers leave out their very last copy, so that a wait runs
+// out, the kernel reports STATUS_WAIT_TIMEOUT and returns.  Nothing faults or hangs.
+extern "C" int fd_tc_test_hook(long long wait_ns, int skip_last) {
+    g_tc_wait_ns = wait_ns > 0 ? (unsigned long long)wait_ns : TC_WAIT_NS;
+    g_tc_skip_last = skip_last ? 1 : 0;
+    return 0;
 }

@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import ctypes
 import struct
-import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -62,8 +61,6 @@ def lib() -> ctypes.CDLL:
         except OSError as e:  # pragma: no cover - environment failure
             raise KernelError(f"cannot load the CUDA kernel library {path}: {e}") from e
         _declare(_lib)
-        if os.environ.get("FD_PDL", "0") == "1":      # experiment knob; see set_pdl
-            _lib.fd_set_pdl(1)
     return _lib
 
 
@@ -85,6 +82,13 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attn_prefill_set_form": [I],
         "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
         "fd_gemm_tc_qkv_rope": [P, P, P, I, P, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+        "fd_gemm_stream_splits": [I, I, I],
+        "fd_gemm_stream_force_2d": [I],
+        "fd_gemm_stream_set_pdl": [I],
+        "fd_gemm_stream_last_map3d": [],
+        "fd_gemm_stream": [P, P, P, I, P, I, I, I, I, I, P, P],
+        "fd_gemm_stream_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+        "fd_tc_test_hook": [LL, I],
         "fd_gemv_splits": [I, I, I, I, I],
         "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P],
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
@@ -306,6 +310,75 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
         mode = GEMV_BF16 if out.dtype == torch.bfloat16 else GEMV_F32
     _check(lib().fd_gemm_tc(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
                             _ptr(out), mode, M, N, K, _ptr(status), _stream()))
+
+
+def gemm_stream_splits(M: int, N: int, K: int) -> int:
+    """CTAs per cluster (splits of K) the streaming tcgen05 product would use; 0 if it does not take
+    the sizes (more than 128 rows of x, K not a multiple of 8)."""
+    return int(lib().fd_gemm_stream_splits(M, N, K))
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, gated: bool = False,
+                splits: int = 0, status: Optional[torch.Tensor] = None) -> None:
+    """Weight-streaming product for up to 128 rows of x on the tcgen05 tensor cores (W tiles as the
+    M side, the rows of x as the N side, K split over a thread-block cluster for narrow W):
+    out = x w^T (+ bias), bfloat16 or float32 [M, N], or with ``gated`` (w rows in tiles of 8 gate +
+    8 up) bfloat16 [M, N / 2] = silu(gate) * up.  ``splits`` 0: chosen by the launcher."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K
+    if gated:
+        assert out.dtype == torch.bfloat16 and out.shape == (M, N // 2) and bias is None
+        mode = GEMV_GATED
+    else:
+        assert out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32)
+        mode = GEMV_BF16 if out.dtype == torch.bfloat16 else GEMV_F32
+    _check(lib().fd_gemm_stream(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                                _ptr(out), mode, M, N, K, splits, _ptr(status), _stream()))
+
+
+def gemm_stream_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                         cos: torch.Tensor, sin: torch.Tensor, tok_row: torch.Tensor, tok_pos: torch.Tensor,
+                         row_slot: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                         n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor,
+                         splits: int = 0) -> None:
+    """The q/k/v projection of a step of up to 128 tokens on the streaming tcgen05 product, with bias,
+    rotary encoding and the append to the paged cache in its epilogue.  ``w`` and ``bias`` in the
+    paired row order (see ``rope_append``)."""
+    M, K = x.shape
+    assert w.shape == ((n_q + 2 * n_kv) * head_dim, K) and q_out.shape == (M, n_q * head_dim)
+    assert x.dtype == w.dtype == q_out.dtype == k_pool.dtype == torch.bfloat16
+    num_blocks, _, block_size, _ = k_pool.shape
+    _check(lib().fd_gemm_stream_qkv_rope(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                                         _ptr(q_out), M, K, splits, _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_row),
+                                         _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                                         block_table.shape[1], num_blocks, block_size, n_q, n_kv, head_dim,
+                                         int(write_kv), _ptr(status), _stream()))
+
+
+def gemm_stream_set_pdl(on: bool) -> None:
+    """Whether the streaming product is launched with the programmatic-dependent-launch attribute (the
+    default): it may then start and fetch its first weights while the kernel before it in the stream
+    still runs, and waits for that kernel before it reads x or writes anything."""
+    lib().fd_gemm_stream_set_pdl(int(on))
+
+
+def gemm_stream_force_2d(on: bool) -> None:
+    """Tests: make the streaming product read its operands through two-dimensional tensor maps (one copy per
+    k-block) even where K is a multiple of 64 and one three-dimensional copy per stage would do."""
+    lib().fd_gemm_stream_force_2d(int(on))
+
+
+def gemm_stream_last_map3d() -> bool:
+    """Whether the last streaming product read its operands through three-dimensional tensor maps."""
+    return bool(lib().fd_gemm_stream_last_map3d())
+
+
+def tc_test_hook(wait_ns: int = 0, skip_last: bool = False) -> None:
+    """Tests only.  The limit of every bounded wait of the TMA + tcgen05 kernels (0: the default of
+    0.2 s) and whether their producers leave out their very last copy, so that a wait runs out and the
+    kernel reports ``STATUS_WAIT_TIMEOUT`` and returns."""
+    lib().fd_tc_test_hook(int(wait_ns), int(skip_last))
 
 
 def gemv_splits(M: int, N: int, K: int, target_ctas: int, allow_split: bool = True) -> int:

@@ -11,7 +11,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import KVRequest, LayerCache, Mixer, Runtime
-from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul
+from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul, stream_gemm
 
 
 MAX_SPLITS = 32
@@ -119,13 +119,18 @@ class GQAAttention(Mixer):
             K.gemv_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
                             lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status,
                             splits)
+        elif self.paired and x.dtype == torch.bfloat16 and stream_gemm(T, self.w_qkv.shape[0], self.hidden_size):
+            # larger decode batches and short prompts: the same fusion in the streaming tcgen05 kernel
+            K.gemm_stream_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos,
+                                   ctx.row_slot, lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d,
+                                   lc.writes, self.rt.status)
         elif self.paired and x.dtype == torch.bfloat16 and fused_prompt_gemm(T, self.w_qkv.shape[0], self.hidden_size):
             # prompts: the same fusion on the tcgen05 tensor cores
             K.gemm_tc_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
                                lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status)
         else:
             qkv = ws.get("qkv", (T, (self.n_q + 2 * self.n_kv) * d), x.dtype)
-            matmul(x, self.w_qkv, self.b_qkv, qkv)
+            matmul(x, self.w_qkv, self.b_qkv, qkv, status=self.rt.status)
             K.rope_append(qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot, lc.k_pool, lc.v_pool,
                           lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status, paired=self.paired)
         attn = ws.get("attn", (T, self.n_q * d), x.dtype)
@@ -140,4 +145,4 @@ class GQAAttention(Mixer):
                          self.n_q, self.n_kv, d, self.scale, self.window or 0, n_splits, split_len, scratch,
                          self.rt.status)
         out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
-        return matmul(attn, self.w_o, None, out, target_ctas=4 * self.rt.sm_count)
+        return matmul(attn, self.w_o, None, out, target_ctas=4 * self.rt.sm_count, status=self.rt.status)

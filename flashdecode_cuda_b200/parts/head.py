@@ -37,5 +37,5 @@ class LinearHead(Head):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         logits = ctx.ws.get("logits", (x.shape[0], self.vocab_size), torch.float32)
-        matmul(x, self.weight, None, logits)
+        matmul(x, self.weight, None, logits, status=self.rt.status)
         return logits

@@ -1,10 +1,13 @@
 """Matrix products of the parts: ``out = x w^T (+ bias)`` with ``w [N, K]``.
 
 float32: the library's own FFMA kernel with a fixed summation order (no
-tensor cores, no reduced-precision mode).  bfloat16 with at most 64 rows of x
-(decode steps): the hand-written weight-streaming kernel (``csrc/gemv_mma.cu``).
-Other bfloat16 products: cuBLAS through torch, which is what ``F.linear`` is in
-davidjoyme/flashdecode-cuda (engine/model.py:188-190,208,213-216,232).
+tensor cores, no reduced-precision mode).  bfloat16 with at most 16 rows of x
+(decode steps): the weight-streaming ``mma.sync`` kernel (``csrc/gemv_mma.cu``);
+17 to 128 rows (larger decode batches, short prompts): the weight-streaming
+TMA + tcgen05 kernel (``csrc/gemm_stream_tcgen05.cu``).  More rows (prompts):
+the TMA + tcgen05 kernel of ``csrc/gemm_tcgen05.cu`` where its fused epilogues
+pay, cuBLAS through torch for the plain products, which is what ``F.linear`` is
+in davidjoyme/flashdecode-cuda (engine/model.py:188-190,208,213-216,232).
 """
 
 from __future__ import annotations
@@ -27,6 +30,14 @@ PROMPT_GEMM = "auto"
 # B200 at the sizes of Qwen2.5-1.5B); above it the rows of x no longer fit the registers' reach.
 GEMV_MAX_ROWS = 16
 MAX_PARTS = 4           # most partial sums the norm's fast kernel adds up
+# Up to this many rows (and above GEMV_MAX_ROWS) the streaming tcgen05 kernel takes the product with
+# its fused epilogues: the rows of x are the N side of its MMAs, so nothing is padded to a 128-row tile.
+STREAM_MAX_ROWS = 128
+
+
+def stream_gemm(M: int, N: int, Kd: int) -> bool:
+    """Whether a bfloat16 product with M rows of x goes to the streaming tcgen05 kernel."""
+    return PROMPT_GEMM == "auto" and GEMV_MAX_ROWS < M <= STREAM_MAX_ROWS and K.gemm_stream_splits(M, N, Kd) > 0
 
 
 def fused_prompt_gemm(M: int, N: int, Kd: int) -> bool:
@@ -38,14 +49,16 @@ def fused_prompt_gemm(M: int, N: int, Kd: int) -> bool:
 
 
 def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-           target_ctas: int = 0, parts: Optional[torch.Tensor] = None) -> torch.Tensor:
+           target_ctas: int = 0, parts: Optional[torch.Tensor] = None,
+           status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K], w [N, K], bias [N] or None, out [M, N] (dtype of x, or
     float32 for logits).  ``target_ctas``: how many CTAs a decode product
     should spread over (it splits K to get there).  ``parts``: float32 memory
     for [splits <= MAX_PARTS, M, N]; when given (no bias) and the product is
     split, the splits' partial sums are returned in it as [splits, M, N] for the
     consumer to add up in order (the next norm does), instead of being added
-    inside a thread-block cluster, whose launch and barriers cost more."""
+    inside a thread-block cluster, whose launch and barriers cost more.
+    ``status``: the status word for the kernels with bounded waits."""
     if x.dtype == torch.float32:
         K.gemm_simt(x, w, bias, out)
         return out
@@ -59,6 +72,9 @@ def matmul(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         if splits >= 1:
             K.gemv(x, w, bias, out, K.GEMV_F32 if out.dtype == torch.float32 else K.GEMV_BF16, splits)
             return out
+    if stream_gemm(M, w.shape[0], Kd):
+        K.gemm_stream(x, w, bias, out, status=status)
+        return out
     if PROMPT_GEMM == "tcgen05" and K.gemm_tc_supported(M, w.shape[0], Kd):
         K.gemm_tc(x, w, bias, out)
         return out

@@ -10,7 +10,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import FeedForward, Runtime
-from .linear import GEMV_MAX_ROWS, MAX_PARTS, fused_prompt_gemm, matmul
+from .linear import GEMV_MAX_ROWS, MAX_PARTS, fused_prompt_gemm, matmul, stream_gemm
 
 
 @register_part("feed_forward", "swiglu")
@@ -52,12 +52,14 @@ class SwiGLU(FeedForward):
         if (self.tiled and x.dtype == torch.bfloat16 and T <= GEMV_MAX_ROWS
                 and K.gemv_splits(T, 2 * self.inter, self.hidden_size, 1, allow_split=False) == 1):
             K.gemv(x, self.w_gate_up, None, act, K.GEMV_GATED)          # product and silu(gate) * up in one kernel
+        elif self.tiled and x.dtype == torch.bfloat16 and stream_gemm(T, 2 * self.inter, self.hidden_size):
+            K.gemm_stream(x, self.w_gate_up, None, act, gated=True, status=self.rt.status)      # 17 to 128 rows: the same fusion
         elif self.tiled and x.dtype == torch.bfloat16 and fused_prompt_gemm(T, 2 * self.inter, self.hidden_size):
             K.gemm_tc(x, self.w_gate_up, None, act, gated=True, status=self.rt.status)     # prompts: tcgen05, same fusion
         else:
             gu = ws.get("gate_up", (T, 2 * self.inter), x.dtype)
-            matmul(x, self.w_gate_up, None, gu)
+            matmul(x, self.w_gate_up, None, gu, status=self.rt.status)
             K.silu_mul(gu, act, tiled=self.tiled)
         out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
         parts = ws.get("ffn_out_parts", (MAX_PARTS, T, self.hidden_size), torch.float32) if T <= GEMV_MAX_ROWS else None
-        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, parts=parts)
+        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, parts=parts, status=self.rt.status)

@@ -201,6 +201,70 @@ def test_gemv_refuses_what_it_cannot_do():
                torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV), K.GEMV_BF16)
 
 
+@pytest.fixture(params=[False, True], ids=["3d", "2d"])
+def stream_maps(request):
+    """The streaming product's copies: one three-dimensional copy per operand and stage where K is a
+    multiple of 64 (the default), or one two-dimensional copy per k-block."""
+    K.gemm_stream_force_2d(request.param)
+    yield request.param
+    K.gemm_stream_force_2d(False)
+
+
+@pytest.mark.parametrize("M", [1, 8, 17, 24, 33, 48, 64, 100, 128])
+@pytest.mark.parametrize("N,K_", [(16, 8), (100, 96), (333, 1536), (2048, 1536), (1536, 8960), (4880, 200), (129, 72),
+                                  (300, 320), (40000, 128)])
+def test_gemm_stream_decode_product(M, N, K_, stream_maps):
+    """The streaming tcgen05 product of decode steps (W tiles as the M side of the MMAs, the rows of x
+    as the N side): every output form, rows of W, rows of x and K that fill no tile, K split over
+    clusters of 2, 4 and 8 CTAs and unsplit with several tiles per persistent CTA."""
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(torch.bfloat16).to(DEV)
+    b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
+    want = P.linear(x.double(), w.double())
+    assert K.gemm_stream_splits(M, N, K_) in (1, 2, 4, 8)
+    st = status()
+    for splits in (0, 1, 2, 4, 8):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K.gemm_stream(x, w, b, out, splits=splits, status=st)
+        assert K.gemm_stream_last_map3d() == (K_ % 64 == 0 and not stream_maps)
+        assert rel(out, want + b.double()) < 5e-3, splits
+        out32 = torch.full((M, N), float("nan"), device=DEV)
+        K.gemm_stream(x, w, None, out32, splits=splits, status=st)
+        assert rel(out32, want) < 2e-5, splits
+        K.gemm_stream(x, w, b.float(), out32, splits=splits, status=st)            # a bias kept in 32-bit
+        assert rel(out32, want + b.double()) < 2e-5, splits
+        if N % 16 == 0:
+            I = N // 2
+            gate, up = w[:I], w[I:]
+            tiled = torch.stack([gate.view(I // 8, 8, K_), up.view(I // 8, 8, K_)], dim=1).reshape(N, K_).contiguous()
+            act = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+            K.gemm_stream(x, tiled, None, act, gated=True, splits=splits, status=st)
+            assert rel(act, P.swiglu(P.linear(x.double(), gate.double()), P.linear(x.double(), up.double()))) < 6e-3, splits
+    assert int(st.item()) == 0
+
+
+def test_gemm_stream_sums_do_not_depend_on_the_batch():
+    """A row of x gives the same bits alone and among 63 others (the split of K and the order in
+    which the cluster adds its partial sums depend on the matrix only)."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(64, 1536, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2048, 1536, generator=g) / 40).to(torch.bfloat16).to(DEV)
+    big = torch.empty(64, 2048, device=DEV)
+    one = torch.empty(1, 2048, device=DEV)
+    K.gemm_stream(x, w, None, big, status=status())
+    K.gemm_stream(x[37:38].contiguous(), w, None, one, status=status())
+    assert torch.equal(big[37:38], one)
+
+
+def test_gemm_stream_refuses_what_it_cannot_do():
+    assert K.gemm_stream_splits(129, 128, 64) == 0 and K.gemm_stream_splits(4, 128, 12) == 0
+    x = torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(K.KernelError, match="multiple of 8"):
+        K.gemm_stream(x, torch.zeros(16, 12, dtype=torch.bfloat16, device=DEV), None,
+                      torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
+
+
 TC_DEFAULT_TILING = 1
 
 
@@ -432,6 +496,58 @@ def test_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
     kp.zero_()
     K.gemv_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, i32([-1] * M), kp, vp, table.to(DEV),
                     n_q, n_kv, d, True, status(), 1)
+    assert float(kp.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,bs,Kd", [(12, 2, 128, 16, 1536), (6, 2, 48, 4, 96), (3, 1, 32, 16, 96),
+                                              (7, 7, 16, 8, 64), (28, 4, 128, 32, 224)])
+@pytest.mark.parametrize("M", [3, 17, 33, 64, 100])
+def test_stream_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
+    """q/k/v product + bias + rotation + cache append in the streaming tcgen05 kernel, unsplit and with K
+    split over clusters, against the plain functions applied to the natural-order weights; some rows
+    of the step are padding (slot -1) and must write nothing."""
+    g = torch.Generator().manual_seed(n_q * 100 + M)
+    bf = torch.bfloat16
+    N = (n_q + 2 * n_kv) * d
+    x = torch.randn(M, Kd, generator=g).to(bf)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(bf)
+    b = (0.5 * torch.randn(N, generator=g)).to(bf)
+    ctx = [int(v) for v in torch.randint(0, 50, (M,), generator=g)]
+    table, slots, total = scrambled_table([c + 1 for c in ctx], bs, M + 2, g)
+    padding = [m for m in range(M) if m % 5 == 4]
+    slots_in = [(-1 if m in padding else s) for m, s in enumerate(slots)]
+    theta, n_pos = 9999.0, 64
+    inv = 1.0 / (theta ** (torch.arange(0, d, 2).float() / d))
+    fr = torch.outer(torch.arange(n_pos).float(), inv)
+    cos, sin = fr.cos().to(DEV), fr.sin().to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tok_row, tok_pos, row_slot = i32(list(range(M))), i32(ctx), i32(slots_in)
+    order = paired_order(n_q, n_kv, d)
+    wp, bp = w[order].contiguous().to(DEV), b[order].contiguous().to(DEV)
+    qkv = (P.linear(x.double(), w.double(), b.double())).view(M, n_q + 2 * n_kv, d)
+    c2, s2 = P.rope_tables(d, n_pos, theta)
+    rot = P.apply_rope(qkv[:, :n_q + n_kv], c2[torch.tensor(ctx)], s2[torch.tensor(ctx)])
+    live = [m for m in range(M) if m not in padding]
+    for splits in (0, 1, 2, 8):
+        for bias in (bp, bp.float()):
+            kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
+            vp = torch.zeros_like(kp)
+            q_out = torch.zeros(M, n_q * d, dtype=bf, device=DEV)
+            st = status()
+            K.gemm_stream_qkv_rope(x.to(DEV), wp, bias, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp,
+                                   table.to(DEV), n_q, n_kv, d, True, st, splits)
+            assert int(st.item()) == 0
+            assert rel(q_out.view(M, n_q, d)[live], rot[live, :n_q]) < 6e-3
+            assert float(q_out.view(M, n_q, d)[padding].abs().max() if padding else 0.0) == 0.0
+            for m in live:
+                blk = int(table[slots[m], ctx[m] // bs])
+                assert rel(kp[blk, :, ctx[m] % bs], rot[m, n_q:]) < 6e-3
+                assert rel(vp[blk, :, ctx[m] % bs], qkv[m, n_q + n_kv:]) < 6e-3
+            assert int((kp != 0).sum().item()) <= len(live) * n_kv * d        # only this step's positions were written
+    # an entry that reads another entry's cache writes no keys
+    kp.zero_()
+    K.gemm_stream_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp, table.to(DEV),
+                           n_q, n_kv, d, False, status())
     assert float(kp.abs().max()) == 0.0
 
 
