@@ -1,5 +1,5 @@
-// Pieces of the decode matrix product shared by its kernels (gemv_mma.cu: one product per
-// launch; decode_stack.cu: the products of a whole stack of layers inside one persistent kernel).
+// Pieces of the decode matrix product of gemv_mma.cu: the mma.sync and streaming-load wrappers, its
+// parameters and its epilogues.
 #pragma once
 
 #include "common.cuh"

@@ -137,7 +137,6 @@ class Model:
         self._staging = _Staging()
         self.trace: Optional[Dict[str, torch.Tensor]] = None    # set to {} to record per-layer activations
         self.last_meta_host: Optional[np.ndarray] = None        # the index array of the last prepared step
-        self._stacks: Dict[int, object] = {}
         self.bound = False
 
     # ------------------------------------------------------------------ build
@@ -197,11 +196,6 @@ class Model:
         for p in self.all_parts():
             p.bind(on_dev, self.rt)
         self.bound = True
-        # runs of layers that one persistent kernel takes in decode steps (engine/decode_stack.py)
-        self._stacks = {}
-        if self.device.type == "cuda" and self.dtype == torch.bfloat16:
-            from .decode_stack import find_stacks
-            self._stacks = find_stacks(self)
         return self
 
     @property
@@ -379,18 +373,11 @@ class Model:
             self.trace["embed"] = resid.detach().float().cpu().clone()
         caches = self._layer_caches(ctx.cache)
         delta = None
-        i = 0
-        while i < len(self.schedule):
-            stack = self._stacks.get(i)
-            if stack is not None and stack.takes(ctx):
-                delta = stack.forward(ctx, resid, delta, caches)
-                i = stack.last + 1
-                continue
-            delta = self.blocks[self.schedule[i].layer].forward(ctx, resid, delta, caches[i])
+        for i, run in enumerate(self.schedule):
+            delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[i])
             if self.trace is not None:
                 d = delta.float().sum(0) if delta.dim() == 3 else delta.float()
                 self.trace[f"layer.{i}"] = (resid + d).cpu()
-            i += 1
         if ctx.n_want == 0:
             return None
         xn = ctx.ws.get("final_normed", (ctx.n_want, self.hidden_size), self.dtype)
@@ -422,6 +409,4 @@ class Model:
         word = int(self.rt.status.item())
         if word:
             self.rt.status.zero_()
-            for stack in self._stacks.values():       # a kernel that gave up leaves its barrier words undefined
-                stack.reset()
             raise RuntimeError(f"a kernel reported: {K.status_message(word)}")

@@ -16,7 +16,6 @@ ordered with torch's own work and can be captured into a CUDA graph.
 from __future__ import annotations
 
 import ctypes
-import struct
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -80,6 +79,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemm_tc_supported": [I, I, I],
         "fd_gemm_tc_set_wide": [I],
         "fd_attn_prefill_set_form": [I],
+        "fd_attn_decode_set_form": [I],
         "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
         "fd_gemm_tc_qkv_rope": [P, P, P, I, P, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemm_stream_splits": [I, I, I],
@@ -98,10 +98,6 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
-        "fd_decode_stack_layer_bytes": [],
-        "fd_decode_stack_params_bytes": [],
-        "fd_decode_stack_plan": [I, I, I, I],
-        "fd_decode_stack": [ctypes.c_char_p, I, I, P],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)
@@ -269,6 +265,14 @@ def attn_prefill_set_form(form: int) -> None:
     for prompts too short to fill the GPU); 0 = the launcher chooses by the number of CTAs.  For tests and
     measurements."""
     lib().fd_attn_prefill_set_form(int(form))
+
+
+def attn_decode_set_form(form: int) -> None:
+    """Which form the tensor-core decode attention takes from now on: 0 = the launcher chooses (keys as
+    the rows of the MMAs for groups of up to 8 query heads, CTAs of eight warps where all of them fit the
+    GPU at one per SM); bit 0: the heads as rows always; bit 1: four warps always; bit 2: eight warps
+    always.  For tests and measurements."""
+    lib().fd_attn_decode_set_form(int(form))
 
 
 def gemm_tc_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
@@ -483,41 +487,6 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     _attention("fd_attention_simt", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start,
                row_q_len, row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits,
                split_len, scratch, status)
-
-
-# ---------------------------------------------------------------------------
-# a stack of decoder layers in one persistent kernel (csrc/decode_stack.cu)
-
-STACK_LAYER_FORMAT = "<10Q2f6i"     # StackLayer: ten pointers, two eps, six ints
-STACK_PARAMS_FORMAT = "<20Q18ifi"   # StackParams: twenty pointers, eighteen ints, the scale, padding
-
-
-def decode_stack_plan(N: int, K_: int, ctas: int, max_splits: int):
-    """(warps per row tile, splits of K) for one product of the persistent decode kernel."""
-    v = lib().fd_decode_stack_plan(N, K_, ctas, max_splits)
-    return v & 0xFF, v >> 8
-
-
-def pack_stack_layer(w_qkv, b_qkv, w_o, w_gate_up, w_down, norm2_w, next_norm_w, k_pool, v_pool, block_table,
-                     eps2: float, eps_next: float, window: int, write_kv: bool) -> bytes:
-    num_blocks, _, block_size, _ = k_pool.shape
-    raw = struct.pack(STACK_LAYER_FORMAT, _ptr(w_qkv), _ptr(b_qkv) or 0, _ptr(w_o), _ptr(w_gate_up), _ptr(w_down),
-                      _ptr(norm2_w), _ptr(next_norm_w) or 0, _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
-                      float(eps2), float(eps_next), int(window), int(write_kv), block_table.shape[1], num_blocks,
-                      block_size, 0)
-    assert len(raw) == lib().fd_decode_stack_layer_bytes()
-    return raw
-
-
-def decode_stack(pointers, ints, scale: float, ctas: int, skip: int = 0) -> None:
-    """Launch the persistent kernel: ``pointers`` are the twenty tensors (or None) of StackParams
-    in its order, ``ints`` its eighteen integers.  ``skip``: phases to leave out, for timing
-    studies only (bit 0 q/k/v, 1 attention, 2 o, 3 gate/up, 4 down, 5 prefetches, 6 norms)."""
-    assert len(pointers) == 20 and len(ints) == 18
-    raw = struct.pack(STACK_PARAMS_FORMAT, *[(_ptr(t) or 0) for t in pointers], *[int(i) for i in ints], float(scale),
-                      int(skip))
-    assert len(raw) == lib().fd_decode_stack_params_bytes()
-    _check(lib().fd_decode_stack(raw, len(raw), ctas, _stream()))
 
 
 _sample_scratch = {}

@@ -19,13 +19,18 @@ MAX_SPLITS = 32
 
 def plan_splits(n_rows: int, n_kv: int, kv_len_bound: int, sm_count: int):
     """How a decode step cuts each sequence's keys: (n_splits, split_len).
-    Enough CTAs for about two per SM; split boundaries are multiples of
-    ``split_len`` in absolute position, so they do not move with the batch's
-    contents (only with its size and the length bound)."""
+    Split boundaries are multiples of ``split_len`` in absolute position, so
+    they do not move with the batch's contents (only with its size and the
+    length bound).  Few (sequence, KV head) pairs: one CTA of eight warps per SM
+    (the kernel takes that form from four splits on, when all CTAs fit the GPU
+    at one per SM); many: about two CTAs of four warps per SM."""
     ctas = max(1, n_rows * n_kv)
     # at most 32 splits: beyond that the merge of the splits costs more than longer splits do (measured at
     # batch 1: 16k context 1.54 ms per step with 32 splits of 512 keys, 1.72 ms with 128 splits of 128)
-    want = max(1, min(MAX_SPLITS, (2 * sm_count) // ctas))
+    if ctas * 4 <= sm_count:
+        want = min(MAX_SPLITS, sm_count // ctas)
+    else:
+        want = max(1, min(MAX_SPLITS, (2 * sm_count) // ctas))
     split_len = -(-kv_len_bound // want)
     split_len = max(128, -(-split_len // 32) * 32)
     n_splits = max(1, -(-kv_len_bound // split_len))

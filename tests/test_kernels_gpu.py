@@ -706,10 +706,19 @@ def test_attention_far_key_stands_out(dtype):
         assert rel(got, want) < TOL[dtype], key_pos
 
 
+@pytest.fixture(params=[0, 1, 2, 4, 5], ids=["auto", "heads_as_rows", "four_warps", "eight_warps", "heads_as_rows_eight_warps"])
+def decode_form(request):
+    """The forms of the tensor-core decode attention: keys or heads as the rows of the MMAs (the first for
+    groups of up to 8 heads only), CTAs of four or eight warps."""
+    K.attn_decode_set_form(request.param)
+    yield request.param
+    K.attn_decode_set_form(0)
+
+
 @pytest.mark.parametrize("n_q,n_kv,d,bs", [(12, 2, 128, 16), (7, 1, 128, 4), (5, 5, 64, 32), (16, 1, 64, 16),
                                            (28, 4, 128, 16), (40, 8, 128, 8), (3, 3, 128, 1)])
 @pytest.mark.parametrize("n_splits,split_len", [(1, 0), (2, 160), (3, 128), (11, 32), (16, 32), (33, 32)])
-def test_attention_decode_tensor_cores(n_q, n_kv, d, bs, n_splits, split_len):
+def test_attention_decode_tensor_cores(n_q, n_kv, d, bs, n_splits, split_len, decode_form):
     """The dispatcher's tensor-core kernel for bfloat16 decode steps: groups that
     are no power of two, cached lengths at tile and split edges, a padding row.
     The CTA that finishes last merges the splits and leaves zeros in padding rows."""
@@ -786,7 +795,7 @@ def test_attention_prompts_tcgen05_window(window, bs, form):
 
 
 @pytest.mark.parametrize("window", [1, 16, 17, 100])
-def test_attention_decode_tensor_cores_window_and_far_key(window):
+def test_attention_decode_tensor_cores_window_and_far_key(window, decode_form):
     got, want, _ = run_attention("bfloat16", 6, 2, 128, 16, ctx=[200, 40, 7], new=[1, 1, 1], window=window,
                                  n_splits=4, split_len=64, fn=K.attention)
     assert rel(got, want) < TOL["bfloat16"]

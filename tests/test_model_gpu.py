@@ -146,36 +146,3 @@ def test_batch_neighbours_change_nothing(engines, folders, dtype):
         assert torch.equal(alone, mine)
     else:
         assert rel_err(mine, alone) < TOL[dtype]
-
-
-@pytest.mark.parametrize("name,n_seqs", [("D", 1), ("D", 3), ("E", 5), ("E", 11), ("D", 16)])
-def test_decode_stack_equals_the_layers_own_kernels(engines, folders, monkeypatch, name, n_seqs):
-    """Decode steps of up to 16 sequences through the persistent kernel that runs all layers at once
-    (head sizes 64 and 128, here with a window on one layer; switched on by FD_DECODE_STACK=1): the
-    same steps through the layers' own kernels give the same logits, and both agree with the plain
-    implementation."""
-    from flashdecode_cuda_b200 import kernels as K
-    eng = engines[(name, "bfloat16")]
-    assert eng.model._stacks and next(iter(eng.model._stacks.values())).last == len(eng.model.schedule) - 1
-    lens = [3 + 37 * i % 150 for i in range(n_seqs)]
-    reqs = prompts_for(TINY[name]["vocab_size"], [l + 24 for l in lens], seed=21)
-    calls = []
-    real = K.decode_stack
-    monkeypatch.setattr(K, "decode_stack", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
-    outs = {}
-    for mode in ("1", "0"):
-        monkeypatch.setenv("FD_DECODE_STACK", mode)
-        calls.clear()
-        cache = eng.model.new_cache(max_tokens=64 * 4 * n_seqs, block_size=16)
-        slots = [cache.admit() for _ in reqs]
-        eng.model.step(cache, slots, [r[:l] for r, l in zip(reqs, lens)], None)
-        steps = []
-        for i in range(24):
-            steps.append(eng.model.step(cache, slots, [[r[l + i]] for r, l in zip(reqs, lens)], "last").clone())
-        outs[mode] = torch.stack(steps)             # [24, n_seqs, V]
-        assert len(calls) == (24 if mode == "1" else 0)
-        eng.model.check_status()
-    assert rel_err(outs["1"], outs["0"]) < 1e-2
-    for j in (0, n_seqs - 1):
-        want = oracle_logits(folders[name], reqs[j])[lens[j]:lens[j] + 24]
-        assert rel_err(outs["1"][:, j], want) < TOL["bfloat16"]
