@@ -203,6 +203,9 @@ class PagedCache:
         """For every (slot, extra tokens): make sure blocks exist for positions
         up to length + extra, in every group.  Nothing changes if any group
         cannot serve the whole request."""
+        listed = [slot for slot, _ in wants]
+        if len(set(listed)) != len(listed):
+            raise ValueError(f"a slot appears twice in one reservation: {listed}")
         plan = []
         need_per_group = [0] * len(self.groups)
         for slot, extra in wants:
@@ -291,6 +294,21 @@ class PagedCache:
                 total += n * g.bytes_per_token()
         return total
 
+    def fragmentation(self) -> float:
+        """Share of the allocated token places that hold no token: the unused tails of the sequences' last
+        blocks (engine/paged_cache.py:366-371 of the reference).  0.0 for an empty cache; window groups count
+        the blocks they still hold."""
+        places = tokens = 0
+        for gi, g in enumerate(self.groups):
+            for rec in self.slots:
+                if rec.state != ACTIVE:
+                    continue
+                held = sum(1 for b in rec.blocks[gi] if b >= 0)
+                places += held * self.block_size
+                first = len(rec.blocks[gi]) - held                 # columns a window group has given back
+                tokens += max(0, rec.length - first * self.block_size)
+        return 0.0 if places == 0 else 1.0 - tokens / places
+
     def blocks_in_use(self) -> List[int]:
         return [g.alloc.num_used for g in self.groups]
 
@@ -322,4 +340,4 @@ class PagedCache:
     def __repr__(self) -> str:
         used = ", ".join(f"{g.alloc.num_used}/{g.num_blocks}" for g in self.groups)
         return (f"PagedCache(slots {self.slot_alloc.num_used}/{self.max_slots}, blocks used [{used}], "
-                f"block_size {self.block_size}, {self.dtype})")
+                f"block_size {self.block_size}, fragmentation {self.fragmentation():.1%}, {self.dtype})")

@@ -21,16 +21,45 @@ class PartSpec:
     prefix: str = ""
 
 
-@dataclass
 class LayerSpec:
-    """One layer: the arrangement (a ``block`` part) and the four parts it
-    arranges.  Different layers of one model may name different mixers and
-    feed-forwards."""
-    block: str
-    norm1: PartSpec
-    mixer: PartSpec
-    norm2: PartSpec
-    feed_forward: PartSpec
+    """One layer: the arrangement (a ``block`` part, by its registry name) and
+    the parts it arranges, by the names the block class gives them.  The block
+    class is built as ``block_cls(**built_parts)``, so which parts a layer has,
+    and how many, is the block's business: the pre-norm block takes ``norm1,
+    mixer, norm2, feed_forward``; another arrangement may take three norms, one
+    norm shared by both sub-layers, or no feed-forward at all.  Different
+    layers of one model may name different blocks, mixers and feed-forwards.
+
+    ``LayerSpec("prenorm", norm1=..., mixer=..., norm2=..., feed_forward=...)``
+    or ``LayerSpec("prenorm", {"norm1": ..., ...})``; the four parts of the
+    pre-norm block may also be given by position, in that order.
+    """
+
+    _PRENORM_ORDER = ("norm1", "mixer", "norm2", "feed_forward")
+
+    def __init__(self, block: str, *positional, **named):
+        self.block = block
+        parts: Dict[str, PartSpec] = {}
+        if len(positional) == 1 and isinstance(positional[0], dict):
+            parts.update(positional[0])
+        elif positional:
+            if len(positional) > len(self._PRENORM_ORDER):
+                raise ValueError("parts given by position are norm1, mixer, norm2, feed_forward; name any others")
+            parts.update(zip(self._PRENORM_ORDER, positional))
+        parts.update(named)
+        for name, spec in parts.items():
+            if not isinstance(spec, PartSpec):
+                raise TypeError(f"part {name!r} of a layer must be a PartSpec, got {type(spec).__name__}")
+        self.parts = parts
+
+    def __getattr__(self, name: str) -> PartSpec:
+        parts = self.__dict__.get("parts", {})
+        if name in parts:
+            return parts[name]
+        raise AttributeError(name)
+
+    def __repr__(self) -> str:
+        return f"LayerSpec({self.block!r}, {self.parts!r})"
 
 
 @dataclass

@@ -47,6 +47,7 @@ class _Graph:
         self.launches = 0
         self.sample_scratch = None
         self.n_rows_real = 0
+        self.logits: Optional[torch.Tensor] = None   # [bucket, vocab] float32: the step's logits, in the graph's workspace
         self.host: Optional[np.ndarray] = None       # the step's index array; only a few slices change per step
         self.meta: Optional[torch.Tensor] = None     # its device copy (fixed address)
 
@@ -54,7 +55,7 @@ class _Graph:
 class GraphDecoder:
     """One-token-per-sequence steps of ``model`` over ``cache`` with sampling,
     through captured graphs.  ``run`` takes host tokens and returns the device
-    tensor of sampled tokens; ``run_device_fed`` feeds the previous step's
+    tensor of sampled tokens; with ``tokens=None`` it feeds the previous step's
     sampled tokens without leaving the device."""
 
     def __init__(self, model: Model, cache: PagedCache):
@@ -80,6 +81,7 @@ class GraphDecoder:
 
     def _body(self, g: _Graph, ctx: StepContext, key: Tuple) -> None:
         logits = self.model.forward(ctx)
+        g.logits = logits
         if key[2]:
             K.sample(logits, g.sampled, scratch=g.sample_scratch)
         else:
@@ -131,10 +133,15 @@ class GraphDecoder:
         ctx = self._prepare(g, key, slots, tokens)
         g.host, g.n_rows_real = self.model.last_meta_host.copy(), len(slots)
         g.meta = g.ws.get("step_meta", (g.host.size,), torch.int32)
-        # one eager run: it allocates the workspace and writes this step's keys
-        # and values; the captured replay below rewrites the same values
+        # One eager run before the capture, which allocates the workspace.  It runs on padding rows only (every
+        # slot -1, which every kernel skips): the real step is the graph's first replay, so neither the cache
+        # nor a mixer's per-sequence state sees this step twice.
+        warm = g.host.copy()
+        warm[3 * B:4 * B] = -1
+        self.model._staging.upload(warm, g.meta)
         self._body(g, ctx, key)
         torch.cuda.synchronize()
+        self.model._staging.upload(g.host, g.meta)
         graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES
         with torch.cuda.graph(graph):
@@ -192,6 +199,11 @@ class GraphDecoder:
         except (ValueError, PoolExhausted):
             pass
         return g.sampled
+
+    def last_logits(self, n: int) -> torch.Tensor:
+        """float32 logits [n, vocab] of the last step's first ``n`` sequences (a view of the graph's workspace,
+        valid until the next call)."""
+        return self.last.logits[:n]
 
     def read_tokens(self, n: int) -> List[int]:
         """The first ``n`` tokens of the last step as host integers (one copy into pinned memory)."""

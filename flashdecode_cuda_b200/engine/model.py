@@ -71,6 +71,8 @@ class StepContext:
     h_slots: List[int] = field(default_factory=list)
     h_q_len: List[int] = field(default_factory=list)
     h_ctx_len: List[int] = field(default_factory=list)
+    # set for every schedule entry: whoever consumes the block's output takes float partial sums [parts, T, H]
+    delta_parts_ok: bool = False
 
 
 class _Staging:
@@ -126,8 +128,7 @@ class Model:
         self.blocks = []
         for ls in blueprint.layers:
             block_cls = part_class("block", ls.block)
-            self.blocks.append(block_cls(self._build(ls.norm1), self._build(ls.mixer),
-                                         self._build(ls.norm2), self._build(ls.feed_forward)))
+            self.blocks.append(block_cls(**{name: self._build(spec) for name, spec in ls.parts.items()}))
         self.final_norm = self._build(blueprint.final_norm)
         self.head = self._build(blueprint.head)
         self.schedule = list(blueprint.schedule)
@@ -217,11 +218,12 @@ class Model:
         states: List[StateSpec] = []
         runs = []                        # per schedule entry: (group index or None, layer in group, writes, {name: state key})
         for i, run in enumerate(self.schedule):
-            mixer = self.blocks[run.layer].mixer
-            req: Optional[KVRequest] = mixer.kv_request()
+            mixer = getattr(self.blocks[run.layer], "mixer", None)
+            req: Optional[KVRequest] = mixer.kv_request() if mixer is not None else None
             if run.cache_from is not None:
                 owner = self.schedule[run.cache_from]
-                oreq = self.blocks[owner.layer].mixer.kv_request()
+                omixer = getattr(self.blocks[owner.layer], "mixer", None)
+                oreq = omixer.kv_request() if omixer is not None else None
                 if (req is None) != (oreq is None) or (req is not None and
                                                        (req.n_kv_heads, req.head_dim, req.window) !=
                                                        (oreq.n_kv_heads, oreq.head_dim, oreq.window)):
@@ -243,7 +245,7 @@ class Model:
                 li = groups[gi]["n_layers"]
                 groups[gi]["n_layers"] += 1
             st = {}
-            for s in mixer.state_requests():
+            for s in (mixer.state_requests() if mixer is not None else []):
                 key = f"run{i}.{s.name}"
                 states.append(StateSpec(key, tuple(s.shape), s.dtype))
                 st[s.name] = key
@@ -374,6 +376,10 @@ class Model:
         caches = self._layer_caches(ctx.cache)
         delta = None
         for i, run in enumerate(self.schedule):
+            # whoever norms next - the next entry's block or the final norm - says whether it takes float
+            # partial sums [parts, T, H] for a delta; a block hands that on to its last sub-layer
+            nxt = self.blocks[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else self.final_norm
+            ctx.delta_parts_ok = bool(getattr(nxt, "accepts_parts", False))
             delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[i])
             if self.trace is not None:
                 d = delta.float().sum(0) if delta.dim() == 3 else delta.float()

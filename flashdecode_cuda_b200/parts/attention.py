@@ -15,6 +15,7 @@ from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul, stream_gemm
 
 
 MAX_SPLITS = 32
+FP32_SPLIT_LEN = 256      # keys per split of a decode step in float32
 
 
 def plan_splits(n_rows: int, n_kv: int, kv_len_bound: int, sm_count: int):
@@ -52,6 +53,12 @@ class GQAAttention(Mixer):
 
     def __init__(self, prefix: str, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: "RotaryHalf", window: Optional[int] = None, bias: Optional[bool] = None):
+        if head_dim < 16 or head_dim > 256 or head_dim % 16 != 0:
+            raise ValueError(f"{prefix}: head size {head_dim} is not taken: the attention kernels take multiples of 16 "
+                             f"from 16 to 256")
+        if n_kv_heads < 1 or n_heads % n_kv_heads != 0 or n_heads // n_kv_heads > 64:
+            raise ValueError(f"{prefix}: {n_heads} query heads for {n_kv_heads} key/value heads: the kernels take whole "
+                             f"groups of up to 64 query heads per key/value head")
         self.prefix = prefix
         self.hidden_size, self.n_q, self.n_kv, self.d = hidden_size, n_heads, n_kv_heads, head_dim
         self.position, self.window, self.bias = position, window, bias
@@ -140,7 +147,15 @@ class GQAAttention(Mixer):
                           lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status, paired=self.paired)
         attn = ws.get("attn", (T, self.n_q * d), x.dtype)
         n_splits, split_len, scratch = 1, 0, None
-        if ctx.max_q_len == 1:
+        if ctx.max_q_len == 1 and x.dtype == torch.float32:
+            # the 32-bit path: splits of a fixed length, so that where a sequence's partial sums are cut - and with
+            # it every bit of its result - depends on nothing but its own length
+            split_len = FP32_SPLIT_LEN
+            n_splits = max(1, -(-ctx.kv_len_bound // split_len))
+            if n_splits > 1:
+                scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, self.n_q, d, n_splits),),
+                                 torch.float32)
+        elif ctx.max_q_len == 1:
             n_splits, split_len = plan_splits(ctx.n_rows, self.n_kv, ctx.kv_len_bound, self.rt.sm_count)
             if n_splits > 1:
                 scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, self.n_q, d, n_splits),),

@@ -21,8 +21,16 @@ Kinds and their ``forward``:
 ``resid`` is the float32 residual stream of the step; ``delta`` the output of
 the previous sub-layer that has not been added to it yet (the deferred add of
 engine/model.py:1-45 in davidjoyme/flashdecode-cuda).  A ``delta`` is [T, H]
-in the activation dtype, or [parts, T, H] float32 partial sums (a matrix
-product split over K) that the norm adds up in order while it adds the rest.
+in the activation dtype.
+
+Partial sums are an agreement between two parts, never a surprise: a mixer or
+feed-forward may return float32 partial sums [parts, T, H] (a matrix product
+split over K, which the consumer adds up in order while it adds the rest) ONLY
+when its caller passes ``parts_ok=True``.  A block passes that for a sub-layer
+whose output goes to a norm with ``accepts_parts = True`` (the built-in RMSNorm),
+and for its last sub-layer when ``ctx.delta_parts_ok`` says that whoever norms
+next - the next block (``Block.accepts_parts``) or the final norm - takes them.
+A norm, block or mixer that knows nothing of this gets plain [T, H] tensors.
 """
 
 from __future__ import annotations
@@ -102,6 +110,8 @@ class Position(Part):
 
 class Norm(Part):
     kind = "norm"
+    # True: ``forward`` takes ``delta`` as float32 partial sums [parts, T, H] as well as [T, H]
+    accepts_parts = False
 
 
 class Mixer(Part):
@@ -119,7 +129,12 @@ class FeedForward(Part):
 
 
 class Block(Part):
+    """An arrangement of parts in one layer.  Built as ``cls(**parts)`` from the named parts of its
+    ``LayerSpec``; ``parts()`` lists them; ``mixer`` (if the block has one) is the part whose
+    ``kv_request`` / ``state_requests`` size the layer's share of the cache."""
     kind = "block"
+    # True: ``forward`` takes the incoming ``delta`` as float32 partial sums [parts, T, H] too
+    accepts_parts = False
 
 
 class Head(Part):

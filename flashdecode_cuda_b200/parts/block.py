@@ -27,9 +27,17 @@ class PreNormBlock(Block):
     def parts(self):
         return [self.norm1, self.mixer, self.norm2, self.feed_forward]
 
+    @property
+    def accepts_parts(self) -> bool:
+        """The incoming delta goes straight to norm1."""
+        return bool(getattr(self.norm1, "accepts_parts", False))
+
     def forward(self, ctx, resid: torch.Tensor, delta: Optional[torch.Tensor], lc: LayerCache) -> torch.Tensor:
         xn = ctx.ws.get("normed", tuple(resid.shape), ctx.rt.dtype)
         self.norm1.forward(ctx, delta, resid, xn)
         d1 = self.mixer.forward(ctx, xn, lc)
         self.norm2.forward(ctx, d1, resid, xn)
+        # float partial sums only if whoever adds this block's output has said it takes them
+        if ctx.delta_parts_ok and getattr(self.feed_forward, "offers_parts", False):
+            return self.feed_forward.forward(ctx, xn, parts_ok=True)
         return self.feed_forward.forward(ctx, xn)

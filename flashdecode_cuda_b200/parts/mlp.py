@@ -19,6 +19,8 @@ class SwiGLU(FeedForward):
     engine/ops.py:201-204 of davidjoyme/flashdecode-cuda).  gate and up are one
     [2I, H] matrix here, so they are one product."""
 
+    offers_parts = True     # forward(..., parts_ok=True) may return float partial sums [parts, T, H]
+
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int):
         self.prefix, self.hidden_size, self.inter = prefix, hidden_size, intermediate_size
 
@@ -46,7 +48,9 @@ class SwiGLU(FeedForward):
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
-    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, ctx, x: torch.Tensor, parts_ok: bool = False) -> torch.Tensor:
+        """delta [T, H]; with ``parts_ok`` (the caller's consumer adds partial sums up) a decode step's down
+        projection may come back as float32 [parts, T, H] instead."""
         T, ws = ctx.T, ctx.ws
         act = ws.get("ffn_act", (T, self.inter), x.dtype)
         if (self.tiled and x.dtype == torch.bfloat16 and T <= GEMV_MAX_ROWS
@@ -61,5 +65,7 @@ class SwiGLU(FeedForward):
             matmul(x, self.w_gate_up, None, gu, status=self.rt.status)
             K.silu_mul(gu, act, tiled=self.tiled)
         out = ws.get("ffn_out", (T, self.hidden_size), x.dtype)
-        parts = ws.get("ffn_out_parts", (MAX_PARTS, T, self.hidden_size), torch.float32) if T <= GEMV_MAX_ROWS else None
+        parts = None
+        if parts_ok and T <= GEMV_MAX_ROWS:
+            parts = ws.get("ffn_out_parts", (MAX_PARTS, T, self.hidden_size), torch.float32)
         return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, parts=parts, status=self.rt.status)

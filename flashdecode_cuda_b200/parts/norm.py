@@ -22,6 +22,8 @@ class RMSNorm(Norm):
     float32 and everything up to the final store is float32.
     """
 
+    accepts_parts = True        # the kernel adds up to four float partial sums in order while it adds the residual
+
     def __init__(self, prefix: str, size: int, eps: float):
         self.name = f"{prefix}.weight"
         self.size, self.eps = size, float(eps)

@@ -146,3 +146,147 @@ def test_batch_neighbours_change_nothing(engines, folders, dtype):
         assert torch.equal(alone, mine)
     else:
         assert rel_err(mine, alone) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,n_seqs", [("D", 17), ("E", 24), ("E", 33), ("D", 64)])
+def test_decode_batches_beyond_16_through_graphs(engines, folders, name, dtype, n_seqs):
+    """Decode steps of 17 to 64 sequences of unequal lengths replayed from captured graphs (the buckets above 16,
+    whose products are the streaming tcgen05 kernel in bfloat16), with sequences that end earlier, so that
+    the batch falls into smaller buckets; every step's logits against the plain implementation."""
+    from flashdecode_cuda_b200.engine.decode import GraphDecoder
+    eng = engines[(name, dtype)]
+    V = TINY[name]["vocab_size"]
+    lens = [2 + (37 * i) % 90 for i in range(n_seqs)]
+    n_dec = [3 + (5 * i) % 7 for i in range(n_seqs)]                 # tokens fed one by one: 3 .. 9
+    reqs = prompts_for(V, [l + k for l, k in zip(lens, n_dec)], seed=31)
+    cache = eng.model.new_cache(max_tokens=64 * 3 * n_seqs, block_size=16, max_slots=n_seqs)
+    slots = [cache.admit() for _ in reqs]
+    eng.model.step(cache, slots, [r[:l] for r, l in zip(reqs, lens)], None)
+    dec = GraphDecoder(eng.model, cache)
+    live = list(range(n_seqs))
+    buckets = set()
+    for step in range(max(n_dec)):
+        for i in [i for i in live if step >= n_dec[i]]:
+            cache.release(slots[i])
+        live = [i for i in live if step < n_dec[i]]
+        dec.run([slots[i] for i in live], [reqs[i][lens[i] + step] for i in live])
+        got = dec.last_logits(len(live)).clone()
+        buckets.add(dec.last.ctx.n_rows)
+        for j, i in enumerate(live):
+            if (i + step) % 3 == 0 or i in (live[0], live[-1]):
+                want = oracle_logits(folders[name], reqs[i])[lens[i] + step]
+                assert rel_err(got[j], want) < TOL[dtype], f"request {i} step {step} among {len(live)}"
+    assert max(buckets) >= n_seqs and len(buckets) >= 2
+    for i in live:
+        cache.release(slots[i])
+    cache.check_invariants()
+    eng.model.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["C", "E"])
+def test_mixed_steps(engines, folders, name, dtype):
+    """Steps in which some sequences bring one token and another brings a prompt, or the next part of a
+    prompt: two sequences decode while a third brings its 200 tokens at once, then a fourth its 300 tokens
+    as 128 + 172."""
+    eng = engines[(name, dtype)]
+    V = TINY[name]["vocab_size"]
+    a, b, c, d = prompts_for(V, [30, 61, 200, 300], seed=41)
+    want = {k: oracle_logits(folders[name], r) for k, r in zip("abcd", (a, b, c, d))}
+    cache = eng.model.new_cache(max_tokens=64 * 12, block_size=16, max_slots=4)
+    sa, sb, sc, sd = (cache.admit() for _ in range(4))
+    pa, pb = 20, 50                                   # tokens of a and b that are in the cache
+    eng.model.step(cache, [sa, sb], [a[:pa], b[:pb]], None)
+
+    def check(got, rows):
+        for g, (k, p) in zip(got, rows):
+            assert rel_err(g, want[k][p]) < TOL[dtype], f"request {k} position {p}"
+
+    # a and b go on by one token each while c brings its whole prompt
+    got = eng.model.step(cache, [sa, sc, sb], [[a[pa]], c, [b[pb]]], [[0], [0, 99, 199], [0]])
+    check(got, [("a", pa), ("c", 0), ("c", 99), ("c", 199), ("b", pb)])
+    # a and b go on while d brings the first 128 tokens of its prompt, then the other 172
+    got = eng.model.step(cache, [sd, sa, sb], [d[:128], [a[pa + 1]], [b[pb + 1]]], "last")
+    check(got, [("d", 127), ("a", pa + 1), ("b", pb + 1)])
+    got = eng.model.step(cache, [sb, sd, sa], [[b[pb + 2]], d[128:], [a[pa + 2]]], [[0], [0, 100, 171], [0]])
+    check(got, [("b", pb + 2), ("d", 128), ("d", 228), ("d", 299), ("a", pa + 2)])
+    # and a chunk of several tokens for a sequence that already decodes, beside single tokens
+    got = eng.model.step(cache, [sa, sb], [a[pa + 3:pa + 8], [b[pb + 3]]], "all")
+    check(got, [("a", pa + 3 + i) for i in range(5)] + [("b", pb + 3)])
+    eng.model.check_status()
+    cache.check_invariants()
+
+
+def test_float32_decode_does_not_depend_on_the_batch(engines, folders):
+    """In float32 a decoded token's logits are the same bits alone and in a batch of eight with longer
+    neighbours: the keys are cut into splits of a fixed length, whatever else is in the step."""
+    eng = engines[("D", "float32")]
+    V = TINY["D"]["vocab_size"]
+    reqs = prompts_for(V, [600, 900, 300, 14, 610, 1000, 257, 512], seed=51)
+    cache = eng.model.new_cache(max_tokens=64 * 70, block_size=16, max_slots=9)
+    s = cache.admit()
+    eng.model.step(cache, [s], [reqs[0][:590]], None)
+    alone = [eng.model.step(cache, [s], [[reqs[0][590 + i]]], "last").clone() for i in range(4)]
+    assert rel_err(alone[3][0], oracle_logits(folders["D"], reqs[0])[593]) < TOL["float32"]
+    cache.release(s)
+    slots = [cache.admit() for _ in reqs]
+    heads = [len(r) - 10 for r in reqs]
+    eng.model.step(cache, slots, [r[:h] for r, h in zip(reqs, heads)], None)
+    order = [3, 5, 0, 1, 2, 4, 6, 7]
+    for i in range(4):
+        got = eng.model.step(cache, [slots[j] for j in order], [[reqs[j][heads[j] + i]] for j in order], "last")
+        assert torch.equal(got[2], alone[i][0]), f"decoded token {i}"
+    eng.model.check_status()
+
+
+REAL_WIDTHS = {
+    # the layer sizes of the three presets (two layers each, the whole vocabulary): groups of 6, 7 and 5 query heads
+    "qwen2.5-1.5b": [40, 33, 140],
+    "qwen2.5-7b": [40, 25, 37],
+    "qwen2.5-14b": [40, 19, 31],
+}
+
+
+@pytest.mark.parametrize("preset", list(REAL_WIDTHS))
+def test_two_layers_at_real_widths(preset):
+    """Two layers at the real widths of a preset with its whole vocabulary, in bfloat16: prompts in one
+    unequal batch (one of them longer than a 128-row tile at the smallest preset), then eight tokens one by
+    one, against the plain implementation (layers in float64 on the CPU; the output head, whose matrix alone is
+    gigabytes in float64, as one float64 product on the GPU)."""
+    from flashdecode_cuda_b200.config import config_from_dict, preset_dict
+    from flashdecode_cuda_b200.engine import Model, random_weights
+    from plain import qwen2_plain as P
+    raw = preset_dict(preset)
+    raw["num_hidden_layers"] = 2
+    if "max_window_layers" in raw:
+        raw["max_window_layers"] = min(raw["max_window_layers"], 2)
+    cfg = config_from_dict(raw)
+    model = Model.from_config(cfg, torch.bfloat16, "cuda")
+    tensors = random_weights(model, 5, torch.bfloat16, device="cuda")
+    model.bind(tensors)
+    V = cfg.vocab_size
+    lens = REAL_WIDTHS[preset]
+    reqs = prompts_for(V, [l + 8 for l in lens], seed=61)
+
+    head = tensors.get("lm_head.weight", tensors["model.embed_tokens.weight"]).double()      # on the GPU
+
+    layers = {k: v.cpu().double() for k, v in tensors.items() if k not in ("lm_head.weight", "model.embed_tokens.weight")}
+
+    def plain_logits(tokens, rows):
+        ids = sorted(set(tokens))                    # only the rows of the embedding table that the request uses
+        small = dict(layers)
+        small["model.embed_tokens.weight"] = tensors["model.embed_tokens.weight"][torch.tensor(ids, device="cuda")].cpu().double()
+        hn = P.hidden_states(raw, small, [ids.index(t) for t in tokens])
+        return (hn[rows].cuda() @ head.T).cpu()
+
+    cache = model.new_cache(max_tokens=64 * 8, block_size=16, max_slots=3)
+    slots = [cache.admit() for _ in reqs]
+    got = [model.step(cache, slots, [r[:l] for r, l in zip(reqs, lens)], "last").clone()]
+    for i in range(8):
+        got.append(model.step(cache, slots, [[r[l + i]] for r, l in zip(reqs, lens)], "last").clone())
+    model.check_status()
+    got = torch.stack(got)                                    # [9, 3, V]
+    for j, (r, l) in enumerate(zip(reqs, lens)):
+        want = plain_logits(r, list(range(l - 1, l + 8)))
+        assert rel_err(got[:, j], want) < TOL["bfloat16"], f"request {j}"

@@ -77,6 +77,11 @@ def test_replay(tmp_path, dtype, name, lengths):
     assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
     files = sorted(int(p.stem) for p in out_dir.glob("*.f32"))
     assert files == sorted(expect)                    # a file exactly for the steps that want something
+    import hashlib
+    manifest = json.loads((out_dir / "manifest.json").read_text())
+    assert manifest["config_sha256"] == hashlib.sha256((folder / "config.json").read_bytes()).hexdigest()
+    assert manifest["dtype"] == dtype and manifest["vocab_size"] == V and manifest["steps"] == len(steps)
+    assert [(f["step"], f["rows"]) for f in manifest["files"]] == [(st, len(expect[st])) for st in sorted(expect)]
     worst = 0.0
     for step, exp in expect.items():
         got = torch.from_numpy(np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(len(exp), V))
