@@ -44,6 +44,7 @@
 #include <tuple>
 
 #include "attention.cuh"
+#include "tcgen05.cuh"        // g_tc_wait_ns, g_tc_skip_last: the limit of the bounded waits and the tests' hook
 
 namespace fd {
 
@@ -63,7 +64,6 @@ constexpr int TA_KTILE = 2 * TA_KSLAB;    // K or V [64][128]
 // 192 KB + barriers, one CTA per SM: two query tiles (Q 32 KB and P 16 KB each) and three key/value tiles
 // in flight (32 KB each); with one query tile per CTA (see the kernel), one Q and four key/value tiles
 constexpr int TA_SMEM = TA_NQ * (TA_QTILE + TA_PTILE) + TA_STAGES * 2 * TA_KTILE + 256;
-constexpr unsigned long long TA_WAIT_NS = 200ull * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t ta_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ unsigned long long ta_ns() {
@@ -71,7 +71,8 @@ __device__ __forceinline__ unsigned long long ta_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool ta_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+__device__ __forceinline__ bool ta_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                        unsigned long long limit_ns) {
     unsigned long long t0 = 0;
     for (uint32_t spins = 0;; ++spins) {
         uint32_t ok;
@@ -84,7 +85,7 @@ __device__ __forceinline__ bool ta_wait(uint32_t bar, uint32_t parity, volatile 
         if ((spins & 63) != 63) continue;                    // the clock and the flag only now and then
         if (*abort_flag) return false;
         if (t0 == 0) t0 = ta_ns();
-        else if (ta_ns() - t0 > TA_WAIT_NS) {
+        else if (ta_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             set_status(status, STATUS_WAIT_TIMEOUT);
             return false;
@@ -162,7 +163,8 @@ __device__ __forceinline__ uint64_t ta_desc_mn(uint32_t addr, uint32_t slab_byte
 template <bool SPLIT>
 __global__ void __launch_bounds__(TA_THREADS, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+                            const __grid_constant__ CUtensorMap map_v, const AttnParams p,
+                            const unsigned long long wait_ns, const int skip_last) {
     // SPLIT: one copy of the one query tile, and the 32 KB that saves as a fourth key/value tile in flight
     constexpr int STAGES = SPLIT ? TA_STAGES + 1 : TA_STAGES;
     constexpr int NQB = SPLIT ? 1 : TA_NQ;
@@ -287,7 +289,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int it = 0; it < n_tiles; ++it) {
             const int s = it % STAGES;
             bool ok = true;
-            if (it >= STAGES) ok = ta_wait(ta_saddr(&kv_empty[s]), ((it / STAGES) - 1) & 1, abort_flag, p.status);
+            if (it >= STAGES) ok = ta_wait(ta_saddr(&kv_empty[s]), ((it / STAGES) - 1) & 1, abort_flag, p.status, wait_ns);
             if (!__all_sync(0xffffffffu, ok && *abort_flag == 0)) break;
             const uint32_t full = ta_saddr(&kv_full[s]);
             if (lane == 0) ta_expect(full, 2 * TA_KTILE);
@@ -301,7 +303,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             __syncwarp();                                      // the expectation is set before any copy can complete
             const int j = lane >> 2, part = lane & 3;
             const int blk = __shfl_sync(0xffffffffu, blk_cur, (g0 + j) & 31);
-            if (j < per_tile) {
+            if (j < per_tile && !(skip_last && it == n_tiles - 1 && lane == 0)) {      // tests: one copy of the last tile never leaves
                 // row of the pool seen as [rows, d]: the (block, head) slab, and the tile's place in a larger block
                 const int r0 = j * box;
                 const int row = (blk * p.n_kv + kvh) * bs + (t0 + r0) % bs;
@@ -313,7 +315,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // giving up: the copies in flight must land before the CTA's shared memory is released
         if (lane == 0 && *abort_flag)
             for (int it = max(0, issued - STAGES); it < issued; ++it)
-                ta_wait(ta_saddr(&kv_full[it % STAGES]), (it / STAGES) & 1, abort_flag + 1, nullptr);
+                ta_wait(ta_saddr(&kv_full[it % STAGES]), (it / STAGES) & 1, abort_flag + 1, nullptr, wait_ns);
     } else if (warp == 1 && lane == 0) {
         // ---- issuer of S = Q K^T ----
         // D float, A and B bf16, M 128, N = 64 keys, both operands K-major.  S of a query tile's j-th key tile
@@ -321,16 +323,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // (s_free) - long before they are done with them - so the next scores are always ready; P V has an
         // issuer of its own (below): one thread issuing both took 0.6 us per tile, between two softmax steps.
         const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        bool ok = ta_wait(ta_saddr(&bars[0]), 0, abort_flag, p.status);
+        bool ok = ta_wait(ta_saddr(&bars[0]), 0, abort_flag, p.status, wait_ns);
         for (int it = 0; ok && it < n_tiles; ++it) {
             const int s = it % STAGES;
-            ok = ta_wait(ta_saddr(&kv_full[s]), (it / STAGES) & 1, abort_flag, p.status);
+            ok = ta_wait(ta_saddr(&kv_full[s]), (it / STAGES) & 1, abort_flag, p.status, wait_ns);
             const uint32_t ks = ta_saddr(kv_s + s * 2 * TA_KTILE);
 #pragma unroll
             for (int qt = 0; qt < TA_NQ; ++qt) {
                 int j;
                 if (!ok || !mine(qt, it, j)) continue;
-                if (j >= 2) ok = ta_wait(ta_saddr(&s_free[qt * 2 + (j & 1)]), ((j >> 1) - 1) & 1, abort_flag, p.status);
+                if (j >= 2) ok = ta_wait(ta_saddr(&s_free[qt * 2 + (j & 1)]), ((j >> 1) - 1) & 1, abort_flag, p.status, wait_ns);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t qa = ta_saddr(q_s + (SPLIT ? 0 : qt) * TA_QTILE);
@@ -352,13 +354,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int it = 0; ok && it < n_tiles; ++it) {
                 const int s = it % STAGES;
                 // the tile's copies have landed (the other issuer saw it long ago; this thread must see it too)
-                ok = ta_wait(ta_saddr(&kv_full[s]), (it / STAGES) & 1, abort_flag, p.status);
+                ok = ta_wait(ta_saddr(&kv_full[s]), (it / STAGES) & 1, abort_flag, p.status, wait_ns);
                 const uint32_t vs = ta_saddr(kv_s + s * 2 * TA_KTILE + TA_KTILE);
 #pragma unroll
                 for (int qt = 0; qt < TA_NQ; ++qt) {
                     int j;
                     if (!ok || !mine(qt, it, j)) continue;
-                    ok = ta_wait(ta_saddr(&p_ready[qt]), j & 1, abort_flag, p.status);
+                    ok = ta_wait(ta_saddr(&p_ready[qt]), j & 1, abort_flag, p.status, wait_ns);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t pa = ta_saddr(p_s + qt * TA_PTILE);
@@ -391,7 +393,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int j = 0; j < n_mine; ++j) {
             const int it = it_lo[qt] + (SPLIT ? 2 * j + qt : j);
             const int t0 = t_begin + it * TA_BN;
-            ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&s_full[qt * 2 + (j & 1)]), (j >> 1) & 1, abort_flag, p.status));
+            ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&s_full[qt * 2 + (j & 1)]), (j >> 1) & 1, abort_flag, p.status, wait_ns));
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float x[TA_BN];
@@ -438,7 +440,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // The previous P V must be complete before P is overwritten and before O is touched;
             // then O *= alpha where a maximum moved
             if (j > 0) {
-                ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (j - 1) & 1, abort_flag, p.status));
+                ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (j - 1) & 1, abort_flag, p.status, wait_ns));
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {
@@ -477,7 +479,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             ta_arrive(ta_saddr(&p_ready[qt]));
         }
-        if (ok && n_mine > 0) ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (n_mine - 1) & 1, abort_flag, p.status));
+        if (ok && n_mine > 0) ok = __all_sync(0xffffffffu, ta_wait(ta_saddr(&o_done[qt]), (n_mine - 1) & 1, abort_flag, p.status, wait_ns));
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         float w_own = l_run > 0.f ? 1.f / l_run : 0.f;          // what this thread's O is multiplied by
         float w_other = 0.f;                                    // SPLIT: and the other group's
@@ -642,10 +644,10 @@ int launch_attn_prefill_tcgen05(const AttnParams& p, int n_rows, int T, int max_
     const bool split = g_ta_form == 2 || (g_ta_form == 0 && shared_ctas < ta_sm_count());
     if (split) {
         dim3 grid(p.n_q, (max_q_len + TA_BM - 1) / TA_BM, n_rows);
-        attn_prefill_tcgen05_kernel<true><<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p);
+        attn_prefill_tcgen05_kernel<true><<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p, g_tc_wait_ns, g_tc_skip_last);
     } else {
         dim3 grid(p.n_q, (max_q_len + TA_ROWS - 1) / TA_ROWS, n_rows);
-        attn_prefill_tcgen05_kernel<false><<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p);
+        attn_prefill_tcgen05_kernel<false><<<grid, TA_THREADS, TA_SMEM, stream>>>(mq, mk, mv, p, g_tc_wait_ns, g_tc_skip_last);
     }
     return check_launch("attention_prefill_tcgen05");
 }

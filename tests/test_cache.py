@@ -180,3 +180,29 @@ def test_lengths_version_moves_with_sequences_and_lengths_only():
     assert v3 != v2
     assert c.admit() == s and c.lengths_version != v3     # the same slot with another sequence
     c.check_invariants()
+
+
+def test_a_slot_listed_twice_is_refused_before_anything_changes():
+    cache = PagedCache([KVGroupSpec(1, 1, 8)], [], num_blocks=8, max_slots=2, max_blocks_per_seq=4, block_size=4,
+                       dtype=torch.float32, device="cpu")
+    s = cache.admit()
+    with pytest.raises(ValueError, match="twice"):
+        cache.reserve([(s, 3), (s, 2)])
+    assert cache.blocks_in_use() == [0]
+    cache.check_invariants()
+    cache.reserve([(s, 3)])
+    cache.check_invariants()
+
+
+def test_fragmentation_counts_the_unused_tails():
+    cache = PagedCache([KVGroupSpec(1, 1, 8)], [], num_blocks=16, max_slots=3, max_blocks_per_seq=8, block_size=4,
+                       dtype=torch.float32, device="cpu")
+    assert cache.fragmentation() == 0.0
+    a, b = cache.admit(), cache.admit()
+    cache.reserve([(a, 5), (b, 8)])
+    cache.advance(a, 5)
+    cache.advance(b, 8)
+    assert cache.fragmentation() == pytest.approx(1 - 13 / 16)        # a: 5 of 8 places, b: 8 of 8
+    cache.release(a)
+    assert cache.fragmentation() == 0.0
+    assert "fragmentation" in repr(cache)

@@ -107,3 +107,30 @@ def test_blueprint_lists_parts_layer_by_layer():
     assert bp.head.params["tied_to"] is None
     tied = ARCHITECTURES["Qwen2ForCausalLM"].blueprint(config_from_dict(TINY["A"]))
     assert tied.head.params["tied_to"] == "model.embed_tokens.weight"
+
+
+def test_sizes_the_kernels_do_not_take_are_refused_when_the_model_is_built():
+    """A head size that is no multiple of 16 passes the configuration (the reference's own tiny model has 8)
+    but no attention kernel takes it: the mixer says so when it is built, not at the first step."""
+    import torch
+    from flashdecode_cuda_b200.engine import Model
+    raw = dict(TINY["A"], head_dim=8)
+    cfg = config_from_dict(raw)
+    with pytest.raises(ValueError, match="head size 8"):
+        Model.from_config(cfg, torch.float32, "cpu")
+    Model.from_config(config_from_dict(dict(TINY["A"], head_dim=48)), torch.float32, "cpu")
+
+
+def test_a_layer_is_a_block_name_and_named_parts():
+    from flashdecode_cuda_b200.engine import LayerSpec, PartSpec
+    n = lambda p: PartSpec("norm", "rmsnorm", dict(size=8, eps=1e-5), p)
+    by_position = LayerSpec("prenorm", n("a"), PartSpec("mixer", "x"), n("b"), PartSpec("feed_forward", "y"))
+    by_name = LayerSpec("prenorm", norm1=n("a"), mixer=PartSpec("mixer", "x"), norm2=n("b"), feed_forward=PartSpec("feed_forward", "y"))
+    assert list(by_position.parts) == list(by_name.parts) == ["norm1", "mixer", "norm2", "feed_forward"]
+    assert by_position.mixer.name == "x" and by_name.norm2.prefix == "b"
+    free = LayerSpec("anything", {"only_norm": n("c")}, extra=n("d"))
+    assert list(free.parts) == ["only_norm", "extra"]
+    with pytest.raises(TypeError):
+        LayerSpec("prenorm", norm1="not a spec")
+    with pytest.raises(AttributeError):
+        by_name.norm3

@@ -611,7 +611,7 @@ def attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window
 
 
 def run_attention(dtype, n_q, n_kv, d, bs, ctx, new, window=0, n_splits=1, split_len=0, seed=7,
-                  spike=None, pad_rows=0, fn=None, qk_scale=1.0, ramp=0.0):
+                  spike=None, pad_rows=0, fn=None, qk_scale=1.0, ramp=0.0, expect_status=0):
     g = torch.Generator().manual_seed(seed)
     dt = DT[dtype]
     lens = [c + n for c, n in zip(ctx, new)]
@@ -648,7 +648,7 @@ def run_attention(dtype, n_q, n_kv, d, bs, ctx, new, window=0, n_splits=1, split
     scale = 1.0 / math.sqrt(d)
     (fn or K.attention_simt)(qp, kp, vp, out, table.to(DEV), tok_row, i32(slots_p), i32(starts), i32(new_p), i32(ctx_p),
                      rows, max(new_p), n_q, n_kv, d, scale, window, n_splits, split_len, scratch, st)
-    assert int(st.item()) == 0
+    assert int(st.item()) == expect_status
     want = attention_reference(q, k_seqs, v_seqs, ctx, new, n_q, n_kv, d, scale, window)
     return out[:T], want, out[T:]
 
@@ -920,3 +920,146 @@ def test_gemm_tcgen05_drawn_shapes():
         assert int(st.item()) == 0
     finally:
         K.gemm_tc_set_wide(TC_DEFAULT_TILING)
+
+
+# ---------------------------------------------------------------------------
+# the status word: an index that a kernel had to skip, and a bounded wait that ran out
+
+def _rotary_case(M, n_q, n_kv, d, bs, Kd, n_pos, seed):
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    N = (n_q + 2 * n_kv) * d
+    x = torch.randn(M, Kd, generator=g).to(bf).to(DEV)
+    order = paired_order(n_q, n_kv, d)
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(bf)[order].contiguous().to(DEV)
+    ctx = [int(v) for v in torch.randint(0, n_pos - 1, (M,), generator=g)]
+    table, slots, total = scrambled_table([c + 1 for c in ctx], bs, M + 2, g)
+    inv = 1.0 / (1e4 ** (torch.arange(0, d, 2).float() / d))
+    fr = torch.outer(torch.arange(n_pos).float(), inv)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
+    return dict(x=x, w=w, cos=fr.cos().to(DEV), sin=fr.sin().to(DEV), tok_row=i32(list(range(M))), tok_pos=i32(ctx),
+                row_slot=i32(slots), kp=kp, vp=torch.zeros_like(kp), table=table.to(DEV), slots=slots, ctx=ctx,
+                q=torch.zeros(M, n_q * d, dtype=bf, device=DEV))
+
+
+ROTARY_KERNELS = {
+    "gemv": lambda c, dims, st: K.gemv_qkv_rope(c["x"], c["w"], None, c["q"], c["cos"], c["sin"], c["tok_row"], c["tok_pos"],
+                                                c["row_slot"], c["kp"], c["vp"], c["table"], *dims, True, st, 1),
+    "stream": lambda c, dims, st: K.gemm_stream_qkv_rope(c["x"], c["w"], None, c["q"], c["cos"], c["sin"], c["tok_row"],
+                                                         c["tok_pos"], c["row_slot"], c["kp"], c["vp"], c["table"], *dims,
+                                                         True, st),
+    "prompt": lambda c, dims, st: K.gemm_tc_qkv_rope(c["x"], c["w"], None, c["q"], c["cos"], c["sin"], c["tok_row"],
+                                                     c["tok_pos"], c["row_slot"], c["kp"], c["vp"], c["table"], *dims, True, st),
+    "separate": lambda c, dims, st: K.rope_append((c["x"] @ c["w"].T).contiguous(), c["q"], c["cos"], c["sin"], c["tok_row"],
+                                                  c["tok_pos"], c["row_slot"], c["kp"], c["vp"], c["table"], *dims, True, st,
+                                                  paired=True),
+}
+
+
+@pytest.mark.parametrize("kernel", list(ROTARY_KERNELS))
+def test_status_bits_of_the_rotary_kernels(kernel):
+    """A token whose place in the cache maps to no block (a -1 in the table under a live length), and a
+    position beyond the rotation table: the kernel skips the access, says so in the status word, writes
+    nothing for that token and everything for the others.  Nothing faults."""
+    dims = (6, 2, 64)
+    M, bs = 12, 16
+    # a missing block
+    c = _rotary_case(M, *dims, bs, 128, 200, seed=1)
+    bad = 5
+    good_blk = int(c["table"][c["slots"][bad], c["ctx"][bad] // bs])
+    c["table"][c["slots"][bad], c["ctx"][bad] // bs] = -1
+    st = status()
+    ROTARY_KERNELS[kernel](c, dims, st)
+    assert int(st.item()) == K.STATUS_BAD_BLOCK
+    assert float(c["kp"][good_blk].float().abs().max()) == 0.0               # nothing written for that token
+    other = 0 if bad else 1
+    blk = int(c["table"][c["slots"][other], c["ctx"][other] // bs])
+    assert float(c["kp"][blk, :, c["ctx"][other] % bs].float().abs().max()) > 0.0
+    # a block number beyond the pool
+    c = _rotary_case(M, *dims, bs, 128, 200, seed=2)
+    c["table"][c["slots"][bad], c["ctx"][bad] // bs] = c["kp"].shape[0] + 7
+    st = status()
+    ROTARY_KERNELS[kernel](c, dims, st)
+    assert int(st.item()) == K.STATUS_BAD_BLOCK
+    # a rotation table shorter than a position
+    c = _rotary_case(M, *dims, bs, 128, 200, seed=3)
+    short = max(c["ctx"])                                                     # the table ends just before the farthest position
+    c["cos"], c["sin"] = c["cos"][:short].contiguous(), c["sin"][:short].contiguous()
+    st = status()
+    ROTARY_KERNELS[kernel](c, dims, st)
+    assert int(st.item()) & K.STATUS_BAD_POSITION
+    assert "rotation table" in K.status_message(int(st.item()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_status_bit_of_attention_over_a_missing_block(dtype):
+    """A -1 in the block table inside a sequence's length: prompt and decode attention (CUDA cores in float32,
+    tensor cores in bfloat16) skip the block, set the status bit and return."""
+    g = torch.Generator().manual_seed(3)
+    dt = DT[dtype]
+    n_q, n_kv, d, bs = 6, 2, 64, 16
+    for new, n_splits, split_len in (([1, 1], 1, 0), ([1, 1], 3, 64), ([40, 9], 1, 0)):
+        ctx = [150, 33]
+        lens = [c + n for c, n in zip(ctx, new)]
+        table, slots, total = scrambled_table(lens, bs, 4, g)
+        table[slots[0], 2] = -1                                               # keys 32..47 of the first sequence
+        kp = torch.randn(total, n_kv, bs, d, generator=g).to(dt).to(DEV)
+        vp = torch.randn(total, n_kv, bs, d, generator=g).to(dt).to(DEV)
+        T = sum(new)
+        q = torch.randn(T, n_q * d, generator=g).to(dt).to(DEV)
+        out = torch.zeros(T, n_q * d, dtype=dt, device=DEV)
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        starts = [0, new[0]]
+        tok_row = i32([0] * new[0] + [1] * new[1])
+        scratch = torch.zeros(max(1, K.attention_scratch_floats(T, n_q, d, n_splits)), device=DEV)
+        st = status()
+        K.attention(q, kp, vp, out, table.to(DEV), tok_row, i32(slots), i32(starts), i32(new), i32(ctx), 2, max(new),
+                    n_q, n_kv, d, 0.125, 0, n_splits, split_len, scratch, st)
+        assert int(st.item()) == K.STATUS_BAD_BLOCK, (new, n_splits)
+        assert bool(torch.isfinite(out.float()).all())
+
+
+def test_bounded_waits_report_and_return(tc_tiling):
+    """The TMA + tcgen05 kernels with their wait limit set to a millisecond and their producers told to leave
+    out their very last copy: the consumer's wait runs out, the kernel sets STATUS_WAIT_TIMEOUT, frees its
+    tensor memory and returns; the next launch, with the hook off, is correct.  Nothing hangs or faults."""
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(200, 256, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(512, 256, generator=g) / 16).to(torch.bfloat16).to(DEV)
+    want = P.linear(x.double(), w.double())
+    out = torch.zeros(200, 512, dtype=torch.bfloat16, device=DEV)
+    xs = x[:40].contiguous()
+    outs = torch.zeros(40, 512, dtype=torch.bfloat16, device=DEV)
+    try:
+        K.tc_test_hook(wait_ns=1_000_000, skip_last=True)
+        st = status()
+        K.gemm_tc(x, w, None, out, status=st)
+        torch.cuda.synchronize()
+        assert int(st.item()) == K.STATUS_WAIT_TIMEOUT
+        for splits in (1, 2):
+            st = status()
+            K.gemm_stream(xs, w, None, outs, splits=splits, status=st)
+            torch.cuda.synchronize()
+            assert int(st.item()) == K.STATUS_WAIT_TIMEOUT, splits
+    finally:
+        K.tc_test_hook()
+    st = status()
+    K.gemm_tc(x, w, None, out, status=st)
+    K.gemm_stream(xs, w, None, outs, status=st)
+    assert int(st.item()) == 0
+    assert rel(out, want) < 5e-3 and rel(outs, want[:40]) < 5e-3
+
+
+@pytest.mark.parametrize("form", [1, 2], ids=["two_tiles", "dealt_keys"])
+def test_bounded_waits_of_the_prompt_attention(form):
+    """The same for the tcgen05 prompt attention: one copy of a CTA's last key tile never leaves, the waits run
+    out one after another, the status bit is set, and the next launch is correct."""
+    run = _attention_in_form(form)
+    try:
+        K.tc_test_hook(wait_ns=1_000_000, skip_last=True)
+        run_attention("bfloat16", 4, 2, 128, 16, ctx=[0], new=[200], fn=run, expect_status=K.STATUS_WAIT_TIMEOUT)
+    finally:
+        K.tc_test_hook()
+    got, want, _ = run_attention("bfloat16", 4, 2, 128, 16, ctx=[0], new=[200], fn=run)
+    assert rel(got, want) < TOL["bfloat16"]

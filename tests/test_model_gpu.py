@@ -290,3 +290,49 @@ def test_two_layers_at_real_widths(preset):
     for j, (r, l) in enumerate(zip(reqs, lens)):
         want = plain_logits(r, list(range(l - 1, l + 8)))
         assert rel_err(got[:, j], want) < TOL["bfloat16"], f"request {j}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_trace_of_every_layer(engines, folders, name, dtype, monkeypatch):
+    """``Model.trace = {}`` records the embedding and the residual stream after every layer; each tensor
+    against the plain implementation's trace of the same name, in execution order, so that the first
+    difference names the layer (the manner of testing/diff.py:98-122 of the reference).  With the trace off
+    (the default) a step records nothing and copies nothing to the host."""
+    from helpers import raw_config, weights_of
+    from plain import qwen2_plain as P
+    eng = engines[(name, dtype)]
+    model = eng.model
+    (p,) = prompts_for(TINY[name]["vocab_size"], [150], seed=71)
+    want = {}
+    P.hidden_states(raw_config(folders[name]), weights_of(folders[name]), p, trace=want)
+    cache = model.new_cache(max_tokens=256, block_size=16)
+    slot = cache.admit()
+    assert model.trace is None
+    copies = []
+    real_cpu = torch.Tensor.cpu
+    monkeypatch.setattr(torch.Tensor, "cpu", lambda t, *a, **k: (copies.append(1), real_cpu(t, *a, **k))[1])
+    model.step(cache, [slot], [p[:100]], None)
+    assert model.trace is None and not copies                    # off: nothing recorded, nothing read back
+    monkeypatch.undo()
+    cache.release(slot)
+    slot = cache.admit()
+    model.trace = {}
+    try:
+        model.step(cache, [slot], [p], "last")
+        got = model.trace
+    finally:
+        model.trace = None
+    names = ["embed"] + [f"layer.{i}" for i in range(TINY[name]["num_hidden_layers"])]
+    assert list(got) == names and list(want) == names
+    tol = {"float32": 2e-5, "bfloat16": 2e-2}[dtype]
+    for n in names:                                              # the first failing name is the layer to look at
+        assert rel_err(got[n], want[n]) < tol, f"first difference at {n}"
+    # decode steps record too (one row per sequence): the last layer of the next token
+    model.trace = {}
+    try:
+        model.step(cache, [slot], [[p[-1]]], "last")
+        assert model.trace["layer.0"].shape == (1, TINY[name]["hidden_size"])
+    finally:
+        model.trace = None
+    model.check_status()

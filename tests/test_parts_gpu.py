@@ -447,3 +447,239 @@ def test_toy_routing_and_another_position_encoding(tmp_path):
         for j, ref in enumerate(want):
             assert rel_err(got[j], ref[heads[j] + i]) < 1e-4
     model.check_status()
+
+
+# ---------------------------------------------------------------------------
+# a third toy architecture: a mixer whose state lives on the device only (its decode steps are replayed from
+# CUDA graphs), a norm and a block that know nothing of partial sums, a block of three norms
+# ---------------------------------------------------------------------------
+
+@fd.register_part("mixer", "toy_running_mean_device")
+class RunningMeanDevice(Mixer):
+    """The same function as ``RunningMean`` above, written with device index arrays only (no host mirror of the
+    step), so ``graph_safe`` stays True and decode steps are captured.  Padding rows (slot -1) change nothing."""
+
+    def __init__(self, prefix, hidden_size):
+        self.prefix, self.H = prefix, hidden_size
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}.mix.weight", (self.H, self.H))]
+
+    def state_requests(self):
+        return [StateSpec("sum", (self.H,), torch.float32)]
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.w = tensors[f"{self.prefix}.mix.weight"]
+
+    def forward(self, ctx, x, lc: LayerCache):
+        state = lc.states["sum"]
+        row = ctx.tok_row.long()
+        slot = ctx.row_slot.long()
+        live = (slot >= 0).float()[:, None]                          # [rows, 1]
+        safe = slot.clamp(min=0)
+        xf = x.float() * live[row]
+        cs = torch.cumsum(xf, 0)
+        start = ctx.row_q_start.long()
+        before = cs[start] - xf[start]                                # sum of all tokens before each row's first
+        sums = cs - before[row] + state[safe][row] * live[row]        # running sum inside each sequence
+        counts = (ctx.tok_pos + 1).float()[:, None]
+        out = ((sums / counts) @ self.w.float().T).to(x.dtype)
+        if lc.writes:
+            last = start + ctx.row_q_len.long() - 1
+            state.index_add_(0, safe, (cs[last] - before) * live)      # padding rows add zero to slot 0
+        return out
+
+
+@fd.register_part("norm", "toy_centered_norm")
+class CenteredNorm(fd.parts.Norm):
+    """resid += delta; out = (resid - mean) * rsqrt(var + eps) * weight, with torch on the device.  It knows
+    nothing of partial sums (``accepts_parts`` stays False), so no part may hand it any."""
+
+    def __init__(self, prefix, size, eps):
+        self.name, self.size, self.eps = f"{prefix}.weight", size, float(eps)
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.size,), "vector", init="norm")]
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.weight = tensors[self.name]
+
+    def forward(self, ctx, delta, resid, out, rows=None, n_out=None, write_resid=True):
+        assert delta is None or delta.dim() == 2, "partial sums were handed to a norm that never asked for them"
+        r = resid if rows is None else resid[rows.long()]
+        if delta is not None:
+            r = r + (delta if rows is None else delta[rows.long()]).float()
+            if write_resid:
+                if rows is None:
+                    resid.copy_(r)
+                else:
+                    resid[rows.long()] = r
+        c = r - r.mean(-1, keepdim=True)
+        out.copy_((c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()).to(out.dtype))
+
+
+@fd.register_part("block", "toy_sandwich")
+class SandwichBlock(fd.parts.Block):
+    """Three norms: x += norm_mid(mixer(norm1(x))); x += feed_forward(norm2(x)).  The mixer's output is normed
+    before it is added, so this block does that add itself; its feed-forward's output is handed on as delta."""
+
+    def __init__(self, norm1, mixer, norm_mid, norm2, feed_forward):
+        self.norm1, self.mixer, self.norm_mid, self.norm2, self.feed_forward = norm1, mixer, norm_mid, norm2, feed_forward
+
+    def parts(self):
+        return [self.norm1, self.mixer, self.norm_mid, self.norm2, self.feed_forward]
+
+    def forward(self, ctx, resid, delta, lc):
+        assert delta is None or delta.dim() == 2, "partial sums were handed to a block that never asked for them"
+        xn = ctx.ws.get("normed", tuple(resid.shape), ctx.rt.dtype)
+        self.norm1.forward(ctx, delta, resid, xn)
+        d1 = self.mixer.forward(ctx, xn, lc)
+        zeros = torch.zeros_like(resid)
+        mid = ctx.ws.get("sandwich_mid", tuple(resid.shape), ctx.rt.dtype)
+        self.norm_mid.forward(ctx, d1, zeros, mid)                    # norm of the mixer's output alone
+        self.norm2.forward(ctx, mid, resid, xn)                       # resid += mid; xn = norm2(resid)
+        return self.feed_forward.forward(ctx, xn)
+
+
+@dataclass
+class Toy3Config:
+    hidden_size: int
+    vocab_size: int
+    intermediate_size: int
+    eps: float
+    architecture: str = "Toy3ForCausalLM"
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d["hidden_size"], d["vocab_size"], d["intermediate_size"], d["eps"])
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                "intermediate_size": self.intermediate_size, "eps": self.eps}
+
+
+def toy3_blueprint(cfg: Toy3Config) -> ModelBlueprint:
+    H = cfg.hidden_size
+    rms = lambda name: PartSpec("norm", "rmsnorm", dict(size=H, eps=cfg.eps), name)
+    centered = lambda name: PartSpec("norm", "toy_centered_norm", dict(size=H, eps=cfg.eps), name)
+    ff = lambda i: PartSpec("feed_forward", "swiglu", dict(hidden_size=H, intermediate_size=cfg.intermediate_size),
+                            f"t3.layers.{i}.ff")
+    mean = lambda i: PartSpec("mixer", "toy_running_mean_device", dict(hidden_size=H), f"t3.layers.{i}")
+    attn = lambda i: PartSpec("mixer", "gqa_attention", dict(hidden_size=H, n_heads=2, n_kv_heads=1, head_dim=16,
+                                                            position="rope", bias=False), f"t3.layers.{i}.attn")
+    layers = [
+        # the built-in arrangement with a stateful mixer; its feed-forward's output goes to the sandwich block
+        LayerSpec("prenorm", norm1=rms("t3.layers.0.n1"), mixer=mean(0), norm2=rms("t3.layers.0.n2"), feed_forward=ff(0)),
+        # five named parts, three of them norms, one of another kind
+        LayerSpec("toy_sandwich", {"norm1": centered("t3.layers.1.n1"), "mixer": attn(1), "norm_mid": rms("t3.layers.1.nm"),
+                                   "norm2": rms("t3.layers.1.n2"), "feed_forward": ff(1)}),
+        # the built-in arrangement whose first norm is the foreign one
+        LayerSpec("prenorm", centered("t3.layers.2.n1"), mean(2), rms("t3.layers.2.n2"), ff(2)),
+    ]
+    return ModelBlueprint(
+        hidden_size=H, vocab_size=cfg.vocab_size,
+        embedding=PartSpec("embedding", "token_table", dict(vocab_size=cfg.vocab_size, hidden_size=H), "t3.embed"),
+        positions={"rope": PartSpec("position", "rotary_half", dict(head_dim=16, theta=100.0, max_positions=256))},
+        layers=layers, schedule=[RunSpec(0), RunSpec(1), RunSpec(2)],
+        final_norm=centered("t3.norm"),
+        head=PartSpec("head", "linear_head", dict(vocab_size=cfg.vocab_size, hidden_size=H, tied_to="t3.embed.weight"),
+                      "t3.head"),
+        max_positions=256)
+
+
+fd.register_architecture("Toy3ForCausalLM", Toy3Config, toy3_blueprint)
+
+
+def toy3_plain(w: Dict[str, torch.Tensor], cfg: Toy3Config, tokens: List[int]) -> torch.Tensor:
+    w = {k: v.double() for k, v in w.items()}
+    S = len(tokens)
+    x = w["t3.embed.weight"][torch.tensor(tokens)]
+    cos, sin = P.rope_tables(16, S, 100.0)
+
+    def centered(h, name):
+        c = h - h.mean(-1, keepdim=True)
+        return c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + cfg.eps) * w[name]
+
+    def ff(i, h):
+        p = f"t3.layers.{i}.ff"
+        return P.linear(P.swiglu(P.linear(h, w[f"{p}.gate_proj.weight"]), P.linear(h, w[f"{p}.up_proj.weight"])),
+                        w[f"{p}.down_proj.weight"])
+
+    def mean_mixer(i, h):
+        return (torch.cumsum(h, 0) / torch.arange(1, S + 1, dtype=torch.float64)[:, None]) @ w[f"t3.layers.{i}.mix.weight"].T
+
+    def attn(i, h):
+        p = f"t3.layers.{i}.attn"
+        q = P.apply_rope(P.linear(h, w[f"{p}.q_proj.weight"]).view(S, 2, 16), cos, sin)
+        k = P.apply_rope(P.linear(h, w[f"{p}.k_proj.weight"]).view(S, 1, 16), cos, sin)
+        v = P.linear(h, w[f"{p}.v_proj.weight"]).view(S, 1, 16)
+        return P.linear(P.causal_gqa_attention(q, k, v, 0.25, None).reshape(S, 32), w[f"{p}.o_proj.weight"])
+
+    x = x + mean_mixer(0, P.rmsnorm(x, w["t3.layers.0.n1.weight"], cfg.eps))
+    x = x + ff(0, P.rmsnorm(x, w["t3.layers.0.n2.weight"], cfg.eps))
+    x = x + P.rmsnorm(attn(1, centered(x, "t3.layers.1.n1.weight")), w["t3.layers.1.nm.weight"], cfg.eps)
+    x = x + ff(1, P.rmsnorm(x, w["t3.layers.1.n2.weight"], cfg.eps))
+    x = x + mean_mixer(2, centered(x, "t3.layers.2.n1.weight"))
+    x = x + ff(2, P.rmsnorm(x, w["t3.layers.2.n2.weight"], cfg.eps))
+    return centered(x, "t3.norm.weight") @ w["t3.embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_parts_that_know_nothing_of_partial_sums_and_state_under_graphs(tmp_path, dtype):
+    """Layers given as named parts (a block of three norms among them); a norm and a block without
+    ``accepts_parts`` next to the built-in feed-forward, which offers partial sums in decode steps: one-token
+    steps must hand them plain tensors.  The stateful mixer keeps its state on the device only, so decode
+    steps are replayed from CUDA graphs: a graph's first step must not run twice on that state."""
+    from flashdecode_cuda_b200.engine.decode import GraphDecoder
+    cfg = Toy3Config(64, 97, 96, 1e-5)
+    folder = tmp_path / "toy3"
+    probe = Model.from_config(cfg, torch.float32, "cpu")
+    assert [type(b).__name__ for b in probe.blocks] == ["PreNormBlock", "SandwichBlock", "PreNormBlock"]
+    assert probe.blocks[0].accepts_parts and not probe.blocks[1].accepts_parts and not probe.blocks[2].accepts_parts
+    tensors = fd.weights.random_tensors(probe.tensor_specs(), 7)
+    fd.weights.write_model_folder(folder, cfg.to_dict(), tensors)
+    eng = fd.load(folder, device="cuda", dtype=dtype)
+    model = eng.model
+    assert model.graph_safe and eng.use_graphs
+    prompts = prompts_for(97, [21, 4, 37], seed=3)
+    n_dec = 9
+    reqs = [p + q for p, q in zip(prompts, prompts_for(97, [n_dec] * 3, seed=4))]
+    want = [toy3_plain(tensors, cfg, r) for r in reqs]
+    tol = TOL[dtype]
+    # eager: whole prompts, then one token each (up to 16 rows: the feed-forward would offer partial sums)
+    cache = model.new_cache(max_tokens=512, block_size=8)
+    slots = [cache.admit() for _ in reqs]
+    got = model.step(cache, slots, prompts, "last")
+    for j, p in enumerate(prompts):
+        assert rel_err(got[j], want[j][len(p) - 1]) < tol
+    for i in range(n_dec):
+        got = model.step(cache, slots, [[r[len(p) + i]] for r, p in zip(reqs, prompts)], "last")
+        for j, p in enumerate(prompts):
+            assert rel_err(got[j], want[j][len(p) + i]) < tol, f"eager, request {j}, decoded token {i}"
+    for s in slots:
+        cache.release(s)
+    # the same through captured graphs: the step that captures a graph is a real step of the sequences, and a
+    # sequence that ends changes the bucket, so graphs are captured in the middle of sequences too
+    slots = [cache.admit() for _ in reqs]
+    model.step(cache, slots, prompts, None)
+    dec = GraphDecoder(model, cache)
+    live = [0, 1, 2]
+    for i in range(n_dec):
+        if i == 4:
+            cache.release(slots[1])
+            live = [0, 2]
+        dec.run([slots[j] for j in live], [reqs[j][len(prompts[j]) + i] for j in live])
+        got = dec.last_logits(len(live)).clone()
+        for k, j in enumerate(live):
+            assert rel_err(got[k], want[j][len(prompts[j]) + i]) < tol, f"graphs, request {j}, decoded token {i}"
+    # and through the entry point, greedy: the tokens of the plain implementation
+    if dtype == "float32":
+        res = eng.generate(prompts, 6)
+        for r, p in zip(res, prompts):
+            seq = list(p)
+            for t in r.tokens:
+                assert t == int(toy3_plain(tensors, cfg, seq)[-1].argmax())
+                seq.append(t)
+    model.check_status()
