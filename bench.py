@@ -475,6 +475,7 @@ def main() -> int:
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill measurement")
     ap.add_argument("--block-size", type=int, default=BLOCK_SIZE, help="tokens of a cache block of the main run")
+    ap.add_argument("--no-fp32", action="store_true", help="skip the float32 point (slow at the larger presets)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: only for --impl reference, to try that arm on a machine without a GPU (float32)")
     args = ap.parse_args()
@@ -524,15 +525,16 @@ def main() -> int:
         points[f"decode_b{args.batch}_block{other}_ms"] = round(r["ms_per_step"], 4)
         points[f"prefill_block{other}_ms"] = round(prefill_run(engine, cfg, 2048, warmup, args.seed, pk, block_size=other)["ms"], 3)
         # the true 32-bit path (fewer steps: it is there for exactness, not for speed)
-        del engine
-        torch.cuda.empty_cache()
-        engine32, _, _ = build_engine(args.preset, args.layers, args.seed, torch.float32)
-        r = decode_run(engine32, args.batch, args.context, min(args.steps, 16), warmup, args.seed, e2e=False,
-                       prompt_range=(args.context * 3 // 4, args.context - 256), block_size=args.block_size, trials=2)
-        points[f"decode_b{args.batch}_fp32"] = round(r["tok_s"], 1)
-        points[f"decode_b{args.batch}_fp32_ms"] = round(r["ms_per_step"], 4)
-        points[f"decode_b{args.batch}_fp32_mean_context"] = round(r["mean_context"], 1)
-        del engine32
+        if not args.no_fp32:
+            del engine
+            torch.cuda.empty_cache()
+            engine32, _, _ = build_engine(args.preset, args.layers, args.seed, torch.float32)
+            r = decode_run(engine32, args.batch, args.context, min(args.steps, 16), warmup, args.seed, e2e=False,
+                           prompt_range=(args.context * 3 // 4, args.context - 256), block_size=args.block_size, trials=2)
+            points[f"decode_b{args.batch}_fp32"] = round(r["tok_s"], 1)
+            points[f"decode_b{args.batch}_fp32_ms"] = round(r["ms_per_step"], 4)
+            points[f"decode_b{args.batch}_fp32_mean_context"] = round(r["mean_context"], 1)
+            del engine32
     clk = clocks.stop()
 
     ms = main_run["ms_per_step"]

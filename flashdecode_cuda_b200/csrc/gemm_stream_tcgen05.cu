@@ -551,33 +551,6 @@ static bool gs_plan(int M, int N, int K, int want_splits, GsPlan* pl) {
     return gs_try(M, N, K, 1, pl);
 }
 
-// Three-dimensional tensor map of a row-major bf16 matrix [rows, cols], cols a multiple of 64:
-// (k inside a block of 64, row, k-block), read in boxes of 64 x box_rows x kb, so that ONE copy brings kb
-// swizzled [box_rows x 64] tiles one after another.  Returns 1 if the driver refuses the layout.
-static int tensor_map_blocks(const void* ptr, int rows, int cols, CUtensorMap* out, int box_rows, int kb) {
-    static std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    auto key = std::make_tuple(ptr, rows, cols, box_rows, kb);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return 1;
-    cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
-    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128u};
-    cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)kb};
-    cuuint32_t elem[3] = {1, 1, 1};
-    CUtensorMap m;
-    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return 1;
-    if (cache.size() > 4096) cache.clear();
-    cache[key] = m;
-    *out = m;
-    return 0;
-}
-
 static int g_gs_last_map3d = 0;
 int g_gs_pdl = 1;           // 1: the kernel is launched with the programmatic-dependent-launch attribute (fd_gemm_stream_set_pdl)
 int g_gs_force_2d = 0;      // tests: two-dimensional copies even where the three-dimensional map applies

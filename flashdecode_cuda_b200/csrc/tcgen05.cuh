@@ -215,4 +215,31 @@ inline int tensor_map(const void* ptr, int rows, int cols, CUtensorMap* out, int
     return 0;
 }
 
+// Three-dimensional tensor map of a row-major bf16 matrix [rows, cols], cols a multiple of 64:
+// (k inside a block of 64, row, k-block), read in boxes of 64 x box_rows x kb, so that ONE copy brings kb
+// swizzled [box_rows x 64] tiles one after another.  Returns 1 if the driver refuses the layout.
+inline int tensor_map_blocks(const void* ptr, int rows, int cols, CUtensorMap* out, int box_rows, int kb) {
+    static std::map<std::tuple<const void*, int, int, int, int>, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    auto key = std::make_tuple(ptr, rows, cols, box_rows, kb);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return 1;
+    cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128u};
+    cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)kb};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1;
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return 0;
+}
+
 }  // namespace fd
