@@ -90,6 +90,8 @@ def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     return float((got - want).abs().max()) / scale
 
 
-# float32: only summation order differs from the float64 ground truth.
-# bfloat16: 2^-8 per rounding, a few tens of roundings on the way to a logit.
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# Relative to the scale of the logits.  Set from what the replay tests measure (tests/test_trace_run_gpu.py prints
+# its worst error: 9.5e-7 in float32, where only the order of summation differs from the float64 ground truth, and
+# 8.3e-3 in bfloat16), with a factor of about ten and 2.4 over them; 2e-2 is also the gate of the reference's own
+# layer-by-layer diff (testing/diff.py:44-50,113).
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
