@@ -476,6 +476,8 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="run only the 2,048-token prefill measurement")
     ap.add_argument("--block-size", type=int, default=BLOCK_SIZE, help="tokens of a cache block of the main run")
     ap.add_argument("--no-fp32", action="store_true", help="skip the float32 point (slow at the larger presets)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32: the main run through the true 32-bit path (with --no-points)")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: only for --impl reference, to try that arm on a machine without a GPU (float32)")
     args = ap.parse_args()
@@ -489,7 +491,8 @@ def main() -> int:
 
     import torch
     pk = peaks()
-    engine, cfg, full_layers = build_engine(args.preset, args.layers, args.seed)
+    engine, cfg, full_layers = build_engine(args.preset, args.layers, args.seed,
+                                            torch.float32 if args.dtype == "float32" else torch.bfloat16)
     clocks = ClockSampler()
     clocks.start()
     if args.prefill_only:
@@ -543,8 +546,9 @@ def main() -> int:
     line = {
         "metric": f"decode_tokens_per_s_batch{args.batch}", "value": round(main_run["tok_s"], 1), "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic: random bf16 weights N(0, 0.02), token ids uniform in [0, vocab)",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32",
+        "data": "synthetic: random weights N(0, 0.02), token ids uniform in [0, vocab)",
         "impl": "ours",
         "config": {
             "model": args.preset, "layers": cfg.num_hidden_layers, "layers_full": full_layers,

@@ -308,16 +308,22 @@ def test_gemm_tcgen05(M, N, K_, tc_tiling):
         assert rel(act, P.swiglu(P.linear(x.double(), gate.double()), P.linear(x.double(), up.double()))) < 6e-3
 
 
-def test_gemm_simt_rows_do_not_depend_on_the_batch():
-    """The same row gives the same bits alone and among 100 others."""
+@pytest.mark.parametrize("N,K_", [(77, 300), (200, 1537), (10000, 520)])
+def test_gemm_simt_rows_do_not_depend_on_the_batch(N, K_):
+    """The same row gives the same bits alone, among 8 and among 100 others: the kernels for up to 16 rows (a
+    narrow and a wide form) and the one for more keep the same chain of k for every output element."""
     g = torch.Generator().manual_seed(5)
-    x = torch.randn(101, 300, generator=g).to(DEV)
-    w = torch.randn(77, 300, generator=g).to(DEV)
-    big = torch.empty(101, 77, device=DEV)
-    one = torch.empty(1, 77, device=DEV)
-    K.gemm_simt(x, w, None, big)
-    K.gemm_simt(x[70:71].contiguous(), w, None, one)
-    assert torch.equal(big[70:71], one)
+    x = torch.randn(101, K_, generator=g).to(DEV)
+    w = torch.randn(N, K_, generator=g).to(DEV)
+    b = torch.randn(N, generator=g).to(DEV)
+    big = torch.empty(101, N, device=DEV)
+    some = torch.empty(9, N, device=DEV)
+    one = torch.empty(1, N, device=DEV)
+    K.gemm_simt(x, w, b, big)
+    K.gemm_simt(x[64:73].contiguous(), w, b, some)
+    K.gemm_simt(x[70:71].contiguous(), w, b, one)
+    assert torch.equal(big[70:71], one) and torch.equal(some[6:7], one)
+    assert rel(big, P.linear(x.double(), w.double(), b.double())) < 2e-5
 
 
 # ---------------------------------------------------------------------------
