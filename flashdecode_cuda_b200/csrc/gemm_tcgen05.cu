@@ -325,18 +325,25 @@ constexpr int TW_BN = 256, TW_STAGES = 4;
 constexpr int TW_B_BYTES = TW_BN * TC_BK * 2;                 // 32 KB
 constexpr int TW_STAGE_BYTES = TC_A_BYTES + TW_B_BYTES;       // 48 KB
 constexpr int TW_SMEM = TW_STAGES * TW_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-constexpr int TW_EPI_WARPS = 8;               // two per quarter of the tensor-memory lanes, 128 columns each
+// The same kernel with 128 x 128 tiles and six stages of 32 KB, for products so small that even these tiles number no
+// more than the SMs (prompts of up to about 1,000 tokens at these widths): twice the CTAs at work, each with half the
+// chain of copies and MMAs (q/k/v with its epilogue at 512 and 1,024 tokens: 16 against 22 us).
+constexpr int TN_BN = 128, TN_STAGES = 6;
+constexpr int TN_SMEM = TN_STAGES * (TC_A_BYTES + TN_BN * TC_BK * 2) + 1024 + 256;
+constexpr int TW_EPI_WARPS = 8;               // two per quarter of the tensor-memory lanes, half of the columns each
 constexpr int TW_THREADS = (2 + TW_EPI_WARPS) * 32;
 
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(TW_THREADS, 1)
 gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const TcParams p, const TcRope ra, const int tiles_m, const int tiles_n) {
+    constexpr int STAGE_BYTES = TC_A_BYTES + BN * TC_BK * 2;
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TW_STAGES * TW_STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
     uint64_t* full = bars;                       // [S] a stage has landed
-    uint64_t* empty = bars + TW_STAGES;          // [S] the MMAs that read a stage are done
-    uint64_t* acc_full = bars + 2 * TW_STAGES;   // [2] an accumulator is complete
+    uint64_t* empty = bars + STAGES;          // [S] the MMAs that read a stage are done
+    uint64_t* acc_full = bars + 2 * STAGES;   // [2] an accumulator is complete
     uint64_t* acc_empty = acc_full + 2;          // [2] the epilogue has read it (one arrival per epilogue warp)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -348,7 +355,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     if (threadIdx.x == 0) {
         abort_flag[0] = 0;
         abort_flag[1] = 0;
-        for (int s = 0; s < TW_STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(s_addr(&full[s]), 1);
             mbar_init(s_addr(&empty[s]), 1);
         }
@@ -359,7 +366,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s_addr(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -372,38 +379,38 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         int it = 0;                                    // k-blocks issued so far, over all tiles
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TW_BN;
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
             for (int k = 0; k < k_iters; ++k, ++it) {
-                const int s = it % TW_STAGES;
-                if (it >= TW_STAGES && !mbar_wait(s_addr(&empty[s]), ((it / TW_STAGES) - 1) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(s_addr(&empty[s]), ((it / STAGES) - 1) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
                 if (*abort_flag) { ok = false; break; }
                 const uint32_t fb = s_addr(&full[s]);
-                mbar_expect_tx(fb, TW_STAGE_BYTES);
-                unsigned char* a = tiles + s * TW_STAGE_BYTES;
+                mbar_expect_tx(fb, STAGE_BYTES);
+                unsigned char* a = tiles + s * STAGE_BYTES;
                 tma_load_2d(s_addr(a), &map_x, fb, k * TC_BK, m0);
                 if (p.skip_last && k == k_iters - 1 && tile + (int)gridDim.x >= n_tiles) continue;       // tests: this CTA's very last copy
-                tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);     // 256 rows of W in one box
+                tma_load_2d(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);     // BN rows of W in one box
             }
         }
         if (*abort_flag) {
-            for (int j = max(0, it - TW_STAGES); j < it; ++j)
-                mbar_wait(s_addr(&full[j % TW_STAGES]), (j / TW_STAGES) & 1, abort_flag + 1, nullptr, p.wait_ns);
+            for (int j = max(0, it - STAGES); j < it; ++j)
+                mbar_wait(s_addr(&full[j % STAGES]), (j / STAGES) & 1, abort_flag + 1, nullptr, p.wait_ns);
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
-        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TW_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         int it = 0, t = 0;
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++t) {
             const int buf = t & 1;
             if (t >= 2 && !mbar_wait(s_addr(&acc_empty[buf]), ((t >> 1) - 1) & 1, abort_flag, p.status, p.wait_ns)) break;
             tc_fence_after();
-            const uint32_t acc = tmem + buf * TW_BN;
+            const uint32_t acc = tmem + buf * BN;
             for (int k = 0; k < k_iters; ++k, ++it) {
-                const int s = it % TW_STAGES;
-                if (!mbar_wait(s_addr(&full[s]), (it / TW_STAGES) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
+                const int s = it % STAGES;
+                if (!mbar_wait(s_addr(&full[s]), (it / STAGES) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t a = s_addr(tiles + s * TW_STAGE_BYTES);
+                const uint32_t a = s_addr(tiles + s * STAGE_BYTES);
                 const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < TC_BK / 16; ++kk)
@@ -421,7 +428,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         int t = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++t) {
             const int buf = t & 1;
-            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TW_BN;
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
             const int m = m0 + quarter * 32 + lane;
             const TcToken tk = tc_token(p, ra, m);
             const bool ok = __all_sync(0xffffffffu, mbar_wait(s_addr(&acc_full[buf]), (t >> 1) & 1, abort_flag, p.status, p.wait_ns)) &&
@@ -429,9 +436,9 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             if (!__all_sync(0xffffffffu, ok)) break;
             tc_fence_after();
 #pragma unroll 1
-            for (int c0 = col_half * (TW_BN / 2); c0 < (col_half + 1) * (TW_BN / 2); c0 += 32) {
+            for (int c0 = col_half * (BN / 2); c0 < (col_half + 1) * (BN / 2); c0 += 32) {
                 uint32_t v[32];
-                tc_ld32(tmem + lane_base + buf * TW_BN + c0, v);
+                tc_ld32(tmem + lane_base + buf * BN + c0, v);
                 tc_wait_ld();
                 tc_store32(p, ra, tk, v, m, n0 + c0);
             }
@@ -445,7 +452,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
     }
 }
 
@@ -461,14 +468,22 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 //    TMA threads and an accumulator to both CTAs' epilogue warps;
 //  * both CTAs' epilogue warps read their own tensor memory and arrive (the peer remotely) on the leader's
 //    `acc_empty` barrier; tensor memory is allocated and freed by one warp of each CTA together.
-constexpr int TP_STAGES = 6;
-constexpr int TP_B_BYTES = 128 * TC_BK * 2;                   // this CTA's half of the W tile: 16 KB
-constexpr int TP_STAGE_BYTES = TC_A_BYTES + TP_B_BYTES;       // 32 KB
-constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+// A stage holds KB k-blocks of 64 (KB = 2 where K is a multiple of 64: each operand's k-blocks then come as ONE copy
+// through a three-dimensional tensor map, 32 KB instead of 16 KB - an SM keeps only a few bulk copies in flight,
+// whatever their size, and with 16 KB copies that bounds the pair at about 70 GB/s per SM, below what its tensor
+// cores consume).  Three stages of 64 KB, or six of 32 KB.
+constexpr int TP_RING_KBLOCKS = 6;
+constexpr int TP_B_BYTES = 128 * TC_BK * 2;                   // this CTA's half of the W tile, one k-block: 16 KB
+constexpr int TP_KBLOCK_BYTES = TC_A_BYTES + TP_B_BYTES;      // 32 KB
+constexpr int TP_SMEM = TP_RING_KBLOCKS * TP_KBLOCK_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -481,9 +496,12 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uin
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+template <int KB>
 __global__ void __launch_bounds__(TW_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const TcParams p, const TcRope ra, const int tiles_m, const int tiles_n) {
+    constexpr int TP_STAGES = TP_RING_KBLOCKS / KB;
+    constexpr int TP_STAGE_BYTES = KB * TP_KBLOCK_BYTES;      // x: KB tiles of 16 KB, then W: KB tiles of 16 KB
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + TP_STAGES * TP_STAGE_BYTES);
@@ -498,7 +516,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int k_iters = (p.K + TC_BK - 1) / TC_BK;
+    const int k_iters = ((p.K + TC_BK - 1) / TC_BK + KB - 1) / KB;       // stages of KB k-blocks (a last one may reach beyond K: zeros)
     const int n_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
@@ -539,9 +557,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 if (leader) mbar_expect_tx(s_addr(&full[s]), 2 * TP_STAGE_BYTES);
                 const uint32_t fb = map_to_rank(s_addr(&full[s]), 0);
                 unsigned char* a = tiles + s * TP_STAGE_BYTES;
-                tma_load_2d_pair(s_addr(a), &map_x, fb, k * TC_BK, m0);
+                if (KB == 1) tma_load_2d_pair(s_addr(a), &map_x, fb, k * TC_BK, m0);
+                else tma_load_3d_pair(s_addr(a), &map_x, fb, 0, m0, k * KB);
                 if (p.skip_last && k == k_iters - 1 && tile + n_pairs >= n_tiles) continue;              // tests: this CTA's very last copy
-                tma_load_2d_pair(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);
+                if (KB == 1) tma_load_2d_pair(s_addr(a + TC_A_BYTES), &map_w, fb, k * TC_BK, n0);
+                else tma_load_3d_pair(s_addr(a + KB * TC_A_BYTES), &map_w, fb, 0, n0, k * KB);
             }
         }
         // Giving up: the copies in flight must land before this CTA's shared memory goes away.  The leader sees
@@ -570,10 +590,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 if (!mbar_wait(s_addr(&full[s]), (it / TP_STAGES) & 1, abort_flag, p.status, p.wait_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t a = s_addr(tiles + s * TP_STAGE_BYTES);
-                const uint64_t adesc = smem_desc_sw128(a), bdesc = smem_desc_sw128(a + TC_A_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk)
-                    tc_mma_pair(acc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kk) != 0);
+                for (int kb = 0; kb < KB; ++kb) {
+                    const uint64_t adesc = smem_desc_sw128(a + kb * TC_A_BYTES), bdesc = smem_desc_sw128(a + KB * TC_A_BYTES + kb * TP_B_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 16; ++kk)
+                        tc_mma_pair(acc, adesc + 2 * kk, bdesc + 2 * kk, idesc, (k | kb | kk) != 0);
+                }
                 tc_commit_pair(s_addr(&empty[s]), 3);          // the stage is free in both CTAs
             }
             if (ok) tc_commit_pair(s_addr(&acc_full[buf]), 3); // the accumulator is complete in both CTAs
@@ -616,7 +639,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 }
 
 // ---- host side ------------------------------------------------------------
-int g_tc_wide = 1;      // 2: the two-SM kernel where N >= 256; 1: the wide one-SM kernel; 0: 128 x 128 tiles, one per CTA
+int g_tc_pair_kb = 0;   // measurements: 1 = the two-SM kernel with one k-block per stage even where two are possible
+int g_tc_wide = 1;      // 2: the two-SM kernel where N >= 256; 1: the persistent one-SM kernel (128 x 256 tiles, or 128 x 128
+                        // where those number no more than the SMs); 3: the same with 128 x 256 tiles always; 0: 128 x 128 tiles, one per CTA
 
 static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRope& ra, cudaStream_t stream,
                      const char* what) {
@@ -624,8 +649,10 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
     static int sms = 0;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TW_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<TW_BN, TW_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, TW_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<TN_BN, TN_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, TN_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM);
         if (e != cudaSuccess) return fail(-3, "gemm_tcgen05: cannot get %d bytes of shared memory: %s", TW_SMEM, cudaGetErrorString(e));
         int dev = 0;
         cudaGetDevice(&dev);
@@ -634,26 +661,39 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
     }
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM;
     const bool wide = g_tc_wide && p.N >= TW_BN;
-    CUtensorMap mx, mw;
-    int rc = tensor_map(x, p.M, p.K, &mx, TC_BM);
-    if (rc != 0) return rc;
     const bool pair = wide && g_tc_wide == 2;
-    rc = tensor_map(w, p.N, p.K, &mw, (wide && !pair) ? TW_BN : TC_BM);
-    if (rc != 0) return rc;
+    // 128 x 128 tiles where even those give no CTA a second tile: twice the CTAs at work.  (Where CTAs would take two
+    // of them in a row, the wider tile is faster: q/k/v of 2,048 tokens 22.5 against 25.3 us.)
+    const bool narrow = wide && !pair && g_tc_wide != 3 && (long long)tiles_m * ((p.N + TN_BN - 1) / TN_BN) <= sms;
+    CUtensorMap mx, mw;
     if (pair) {
         const int tiles_m2 = (p.M + 2 * TC_BM - 1) / (2 * TC_BM), tiles_n = (p.N + TW_BN - 1) / TW_BN;
         const long long n_tiles = (long long)tiles_m2 * tiles_n;
         FD_REQUIRE(n_tiles < (1ll << 30), -2, "gemm_tcgen05: %lld tiles", n_tiles);
         const int pairs = (int)(n_tiles < sms / 2 ? n_tiles : sms / 2);
-        return launch(what, gemm_tcgen05_pair_kernel, dim3(2 * pairs), dim3(TW_THREADS), TP_SMEM, stream, dim3(2, 1, 1), mx, mw, p, ra,
+        // two k-blocks per copy where the three-dimensional view of the operands exists
+        if (p.K % 64 == 0 && p.K >= 128 && g_tc_pair_kb != 1 && tensor_map_blocks(x, p.M, p.K, &mx, TC_BM, 2) == 0 &&
+            tensor_map_blocks(w, p.N, p.K, &mw, TC_BM, 2) == 0)
+            return launch(what, gemm_tcgen05_pair_kernel<2>, dim3(2 * pairs), dim3(TW_THREADS), TP_SMEM, stream, dim3(2, 1, 1), mx, mw,
+                          p, ra, tiles_m2, tiles_n);
+        int rc = tensor_map(x, p.M, p.K, &mx, TC_BM);
+        if (rc == 0) rc = tensor_map(w, p.N, p.K, &mw, TC_BM);
+        if (rc != 0) return rc;
+        return launch(what, gemm_tcgen05_pair_kernel<1>, dim3(2 * pairs), dim3(TW_THREADS), TP_SMEM, stream, dim3(2, 1, 1), mx, mw, p, ra,
                       tiles_m2, tiles_n);
     }
+    int rc = tensor_map(x, p.M, p.K, &mx, TC_BM);
+    if (rc != 0) return rc;
+    rc = tensor_map(w, p.N, p.K, &mw, (wide && !narrow) ? TW_BN : TC_BM);
+    if (rc != 0) return rc;
     if (wide) {
-        const int tiles_n = (p.N + TW_BN - 1) / TW_BN;
+        const int bn = narrow ? TN_BN : TW_BN;
+        const int tiles_n = (p.N + bn - 1) / bn;
         const long long n_tiles = (long long)tiles_m * tiles_n;
         FD_REQUIRE(n_tiles < (1ll << 30), -2, "gemm_tcgen05: %lld tiles", n_tiles);
         const int grid = (int)(n_tiles < sms ? n_tiles : sms);
-        gemm_tcgen05_wide_kernel<<<grid, TW_THREADS, TW_SMEM, stream>>>(mx, mw, p, ra, tiles_m, tiles_n);
+        if (narrow) gemm_tcgen05_wide_kernel<TN_BN, TN_STAGES><<<grid, TW_THREADS, TN_SMEM, stream>>>(mx, mw, p, ra, tiles_m, tiles_n);
+        else gemm_tcgen05_wide_kernel<TW_BN, TW_STAGES><<<grid, TW_THREADS, TW_SMEM, stream>>>(mx, mw, p, ra, tiles_m, tiles_n);
         return check_launch(what);
     }
     dim3 grid((p.N + TC_BN - 1) / TC_BN, tiles_m);
@@ -666,15 +706,21 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
 
 using namespace fd;
 
-// Which tiling the products use from now on (1: wide persistent kernel where N >= 256, the default;
-// 0: 128 x 128 tiles only).  For tests and measurements.
+// Which tiling the products use from now on where N >= 256 (1, the default: persistent CTAs with 128 x 256 tiles, or
+// with 128 x 128 tiles where those number no more than the SMs; 3: persistent CTAs with 128 x 256 tiles always; 2: two
+// SMs per 256 x 256 tile; 0: 128 x 128 tiles, one per CTA, everywhere).  For tests and measurements.
 extern "C" int fd_gemm_tc_set_wide(int on) {
-    g_tc_wide = on < 0 ? 0 : (on > 2 ? 2 : on);
+    g_tc_wide = on < 0 ? 0 : (on > 3 ? 3 : on);
     return 0;
 }
 
 // 1 if the tensor-core product takes these sizes (K a multiple of 8, enough rows to be worth a
 // 128-row tile), else 0.
+extern "C" int fd_gemm_tc_pair_kb(int kb) {
+    g_tc_pair_kb = kb;
+    return 0;
+}
+
 extern "C" int fd_gemm_tc_supported(int M, int N, int K) {
     return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && encode_fn() != nullptr;
 }

@@ -78,6 +78,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemm_tc_supported": [I, I, I],
         "fd_gemm_tc_set_wide": [I],
+        "fd_gemm_tc_pair_kb": [I],
         "fd_attn_prefill_set_form": [I],
         "fd_attn_decode_set_form": [I],
         "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
@@ -254,7 +255,8 @@ GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
 def gemm_tc_set_wide(on) -> None:
     """Which tiling ``gemm_tc`` and ``gemm_tc_qkv_rope`` use from now on where N >= 256: 2 = two SMs per
     256 x 256 tile (``tcgen05.mma.cta_group::2``), 1 / True = one persistent CTA per SM with 128 x 256
-    tiles, 0 / False = 128 x 128 tiles, one per CTA, everywhere.  For tests and measurements."""
+    tiles, or with 128 x 128 tiles where those number no more than the SMs, 3 = 128 x 256 tiles
+    always, 0 / False = 128 x 128 tiles, one per CTA, everywhere.  For tests and measurements."""
     lib().fd_gemm_tc_set_wide(int(on))
 
 

@@ -268,10 +268,11 @@ def test_gemm_stream_refuses_what_it_cannot_do():
 TC_DEFAULT_TILING = 1
 
 
-@pytest.fixture(params=[2, 1, 0], ids=["pair", "wide", "square"])
+@pytest.fixture(params=[2, 3, 1, 0], ids=["pair", "wide", "auto", "square"])
 def tc_tiling(request):
-    """The tilings of the tcgen05 product: two SMs per 256 x 256 tile, 128 x 256 persistent (both for
-    N >= 256) and 128 x 128."""
+    """The tilings of the tcgen05 product: two SMs per 256 x 256 tile, persistent CTAs with 128 x 256 tiles, the
+    default (persistent CTAs with 128 x 128 tiles where those number no more than the SMs: most shapes of these
+    tests), and 128 x 128 tiles with one CTA each."""
     K.gemm_tc_set_wide(request.param)
     yield request.param
     K.gemm_tc_set_wide(TC_DEFAULT_TILING)
@@ -904,17 +905,17 @@ def test_attention_decode_drawn_shapes():
 
 
 def test_gemm_tcgen05_drawn_shapes():
-    """The three tilings of the tcgen05 product at drawn M, N, K: around the tile edges, fewer rows than one
+    """The four tilings of the tcgen05 product at drawn M, N, K: around the tile edges, fewer rows than one
     CTA of a pair holds, N between one and two wide tiles, K that is no multiple of the 64-wide stage."""
     import random
     rnd = random.Random(13)
     st = status()
     try:
-        for case in range(45):
+        for case in range(60):
             M = rnd.choice([1, 17, 127, 128, 129, 255, 256, 257, 300, 512, 1000, rnd.randint(1, 2500)])
             N = rnd.choice([16, 256, 272, 384, 511, 512, 528, 1536, 2048, rnd.randint(1, 300) * 16])
             K_ = rnd.choice([8, 64, 72, 128, 200, 1536, rnd.randint(1, 200) * 8])
-            tiling = case % 3
+            tiling = case % 4
             K.gemm_tc_set_wide(tiling)
             g = torch.Generator().manual_seed(case)
             x = torch.randn(M, K_, generator=g).to(torch.bfloat16).to(DEV)
