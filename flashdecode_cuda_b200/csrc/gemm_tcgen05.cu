@@ -639,7 +639,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 }
 
 // ---- host side ------------------------------------------------------------
-int g_tc_pair_kb = 0;   // measurements: 1 = the two-SM kernel with one k-block per stage even where two are possible
 int g_tc_wide = 1;      // 2: the two-SM kernel where N >= 256; 1: the persistent one-SM kernel (128 x 256 tiles, or 128 x 128
                         // where those number no more than the SMs); 3: the same with 128 x 256 tiles always; 0: 128 x 128 tiles, one per CTA
 
@@ -672,7 +671,7 @@ static int launch_tc(const void* x, const void* w, const TcParams& p, const TcRo
         FD_REQUIRE(n_tiles < (1ll << 30), -2, "gemm_tcgen05: %lld tiles", n_tiles);
         const int pairs = (int)(n_tiles < sms / 2 ? n_tiles : sms / 2);
         // two k-blocks per copy where the three-dimensional view of the operands exists
-        if (p.K % 64 == 0 && p.K >= 128 && g_tc_pair_kb != 1 && tensor_map_blocks(x, p.M, p.K, &mx, TC_BM, 2) == 0 &&
+        if (p.K % 64 == 0 && p.K >= 128 && tensor_map_blocks(x, p.M, p.K, &mx, TC_BM, 2) == 0 &&
             tensor_map_blocks(w, p.N, p.K, &mw, TC_BM, 2) == 0)
             return launch(what, gemm_tcgen05_pair_kernel<2>, dim3(2 * pairs), dim3(TW_THREADS), TP_SMEM, stream, dim3(2, 1, 1), mx, mw,
                           p, ra, tiles_m2, tiles_n);
@@ -716,11 +715,6 @@ extern "C" int fd_gemm_tc_set_wide(int on) {
 
 // 1 if the tensor-core product takes these sizes (K a multiple of 8, enough rows to be worth a
 // 128-row tile), else 0.
-extern "C" int fd_gemm_tc_pair_kb(int kb) {
-    g_tc_pair_kb = kb;
-    return 0;
-}
-
 extern "C" int fd_gemm_tc_supported(int M, int N, int K) {
     return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && encode_fn() != nullptr;
 }

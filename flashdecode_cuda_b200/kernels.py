@@ -78,7 +78,6 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_gemm_tc_supported": [I, I, I],
         "fd_gemm_tc_set_wide": [I],
-        "fd_gemm_tc_pair_kb": [I],
         "fd_attn_prefill_set_form": [I],
         "fd_attn_decode_set_form": [I],
         "fd_gemm_tc": [P, P, P, I, P, I, I, I, I, P, P],
