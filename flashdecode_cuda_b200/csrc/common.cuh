@@ -92,6 +92,7 @@ int check_launch(const char* what);
 
 namespace fd {
 extern int g_pdl;      // 1: launches carry the programmatic-serialization attribute (runtime.cu)
+extern unsigned long long g_launches;      // kernels of this library launched so far (runtime.cu)
 
 // Launch with the attributes this library uses: programmatic dependent launch (when enabled)
 // and an optional thread-block cluster shape.
@@ -121,6 +122,7 @@ inline int launch(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 bl
     cfg.numAttrs = n;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
     if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    ++g_launches;
     return 0;
 }
 }  // namespace fd

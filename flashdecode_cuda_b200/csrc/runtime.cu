@@ -13,6 +13,7 @@ extern "C" const char* fd_last_error() { return g_error; }
 namespace fd {
 
 int g_pdl = 0;
+unsigned long long g_launches = 0;
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -22,9 +23,11 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+// After a kernel<<<...>>> launch: its error, if any; counts the launch otherwise.
 int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(-100, "%s: launch failed: %s", what, cudaGetErrorString(e));
+    ++g_launches;
     return 0;
 }
 
@@ -46,6 +49,10 @@ extern "C" int fd_sm_count() {
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     return n;
 }
+
+// Kernels of this library launched so far by this process (every launch goes through fd::launch or
+// fd::check_launch), captured launches included: one count per launch call, not per replay of a graph.
+extern "C" unsigned long long fd_launch_count() { return fd::g_launches; }
 
 // Turn programmatic dependent launch on (1) or off (0, the default) for later launches.
 extern "C" int fd_set_pdl(int on) {

@@ -143,10 +143,10 @@ class GraphDecoder:
         torch.cuda.synchronize()
         self.model._staging.upload(g.host, g.meta)
         graph = torch.cuda.CUDAGraph()
-        before = K.LAUNCHES
+        before = K.launch_count()
         with torch.cuda.graph(graph):
             self._body(g, ctx, key)
-        g.launches = K.LAUNCHES - before          # this library's kernels in one replay
+        g.launches = K.launch_count() - before          # this library's kernels in one replay
         g.graph, g.ctx = graph, ctx
         self.graphs[key] = g
         return g, ctx

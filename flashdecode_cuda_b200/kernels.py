@@ -35,7 +35,6 @@ _STATUS_TEXT = {
 }
 
 _lib: Optional[ctypes.CDLL] = None
-LAUNCHES = 0        # kernels of this library launched so far (bench.py reports the count)
 
 
 class KernelError(RuntimeError):
@@ -104,16 +103,22 @@ def _declare(L: ctypes.CDLL) -> None:
         fn.argtypes = args
         fn.restype = I
     L.fd_attn_scratch_floats.argtypes = [I, I, I, I]
+    L.fd_launch_count.restype = c_ulonglong
+    L.fd_launch_count.argtypes = []
     L.fd_attn_scratch_floats.restype = LL
     L.fd_sample_scratch_words.argtypes = [I, I]
     L.fd_sample_scratch_words.restype = LL
 
 
-def _check(rc: int, kernels: int = 1) -> None:
-    global LAUNCHES
+def _check(rc: int) -> None:
     if rc != 0:
         raise KernelError(lib().fd_last_error().decode())
-    LAUNCHES += kernels
+
+
+def launch_count() -> int:
+    """Kernels of this library launched so far by this process, counted where they are launched (a kernel
+    captured into a graph counts once, at capture)."""
+    return int(lib().fd_launch_count())
 
 
 def _stream() -> int:
@@ -448,7 +453,7 @@ def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, 
         fused = n_splits > 1 and max_q_len == 1 and q.dtype == torch.bfloat16
         args.append(_ptr(_counters(q.device, n_rows * n_kv)) if fused else None)
     args += [_ptr(status), _stream()]
-    _check(getattr(lib(), fn_name)(*args), kernels=2 if n_splits > 1 else 1)
+    _check(getattr(lib(), fn_name)(*args))
 
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
@@ -517,5 +522,4 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
     if words:
         assert scratch.dtype == torch.int32 and scratch.numel() >= words
     _check(lib().fd_sample(_ptr(logits), n, V, _ptr(temperature), _ptr(request), _ptr(step),
-                           seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _ptr(scratch) if words else None, _stream()),
-           kernels=2 if words else 1)
+                           seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _ptr(scratch) if words else None, _stream()))

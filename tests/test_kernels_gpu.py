@@ -964,6 +964,27 @@ ROTARY_KERNELS = {
 }
 
 
+def test_launch_count_counts_kernels_where_they_are_launched():
+    """``launch_count`` rises by one for a product, by one for a decode attention that merges its own splits, by
+    two for the float32 attention with splits (its merge is a kernel of its own), and by nothing for a call that
+    the launcher refuses."""
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(4, 32, dtype=torch.bfloat16, device=DEV)
+    n0 = K.launch_count()
+    K.gemv(x, w, None, out, K.GEMV_BF16)
+    assert K.launch_count() == n0 + 1
+    run_attention("bfloat16", 6, 2, 128, 16, ctx=[300, 40], new=[1, 1], n_splits=3, split_len=128, fn=K.attention)
+    assert K.launch_count() == n0 + 2
+    run_attention("float32", 6, 2, 128, 16, ctx=[300, 40], new=[1, 1], n_splits=3, split_len=128, fn=K.attention)
+    assert K.launch_count() == n0 + 4
+    with pytest.raises(K.KernelError):
+        K.gemm_stream(torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV), torch.zeros(16, 12, dtype=torch.bfloat16, device=DEV),
+                      None, torch.zeros(4, 16, dtype=torch.bfloat16, device=DEV))
+    assert K.launch_count() == n0 + 4
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("kernel", list(ROTARY_KERNELS))
 def test_status_bits_of_the_rotary_kernels(kernel):
     """A token whose place in the cache maps to no block (a -1 in the table under a live length), and a
