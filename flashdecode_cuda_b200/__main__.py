@@ -13,7 +13,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
 import sys
 import time
 
@@ -79,8 +78,7 @@ def main(argv=None) -> int:
     g.add_argument("--sample-seed", type=int, default=0)
     g.add_argument("--stop-ids", default="", help="comma-separated stop token ids (default: eos_token_id of a loaded model)")
     g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "bf16", "float32", "fp32"])
-    g.add_argument("--block-size", type=int, default=int(os.environ.get("FD_BLOCK_SIZE", "64")),
-                   help="tokens per cache block (default: $FD_BLOCK_SIZE or 64)")
+    g.add_argument("--block-size", type=int, default=64, help="tokens per cache block")
     g.add_argument("--max-batch", type=int, default=0, help="sequences that run together (default: all, up to 64)")
     g.add_argument("--max-context", type=int, default=0, help="longest sequence the cache is sized for")
     g.add_argument("--device", default="cuda")
