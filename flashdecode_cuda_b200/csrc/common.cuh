@@ -83,6 +83,23 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 }  // namespace fd
 
+namespace fd {
+// This CTA's share (by its place in the grid) of `bytes` at `ptr` (16-byte aligned) that a later kernel will stream:
+// asked for from L2 as bulk prefetches of up to 16 KB.  Called by ONE thread of every CTA of the grid.
+__device__ __forceinline__ void l2_prefetch_share(const unsigned char* ptr, unsigned long long bytes) {
+    const unsigned long long n_ctas = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+    const unsigned long long cta = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    const unsigned long long per = ((bytes + n_ctas - 1) / n_ctas + 127) & ~127ull;
+    const unsigned long long lo = cta * per;
+    if (lo >= bytes) return;
+    const unsigned long long hi = lo + per < bytes ? lo + per : (bytes & ~15ull);
+    for (unsigned long long o = lo; o < hi; o += 16384) {
+        const unsigned n = (unsigned)(hi - o < 16384 ? hi - o : 16384);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(ptr + o), "r"(n) : "memory");
+    }
+}
+}  // namespace fd
+
 // error reporting shared by the launchers (defined in runtime.cu)
 extern "C" const char* fd_last_error();
 namespace fd {

@@ -127,6 +127,7 @@ gemv_mma_kernel(const GemvParams p, const RopeArgs ra) {
     }
 
     if (!pre_done) rope_prefetch_rest<NT>(p, ra, row0, r, pre);       // a warp without a chunk of its own
+    if (p.pf_bytes != 0 && tid == W * 32 - 1) l2_prefetch_share(p.pf_ptr, p.pf_bytes);
     if (WK > 1) {
         // add the K slices of a row tile in the order wk = 0, 1, ...
         float* mine = red + (warp * 32 + lane) * NT * 4;
@@ -263,6 +264,7 @@ extern "C" int fd_gemv(const void* x, const void* w, const void* bias, int bias_
     GemvParams p;
     p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = out;
     p.M = M; p.N = N; p.K = K; p.n_splits = n_splits; p.mode = mode; p.bias_f32 = bias_f32;
+    p.pf_ptr = nullptr; p.pf_bytes = 0;
     RopeArgs ra = {};
     return run_gemv(p, ra, stream);
 }
@@ -271,14 +273,16 @@ extern "C" int fd_gemv(const void* x, const void* w, const void* bias, int bias_
 // encoding of q and k (float), q to q_out [M, n_q d], k and v into the paged
 // cache at each token's position.  W [(n_q + 2 n_kv) d, K] and bias must have
 // the rows of every q and k head in tiles of 8 dims + their 8 partners (see
-// RopeArgs).  Up to 8 splits of K add up inside a cluster.
+// RopeArgs).  Up to 8 splits of K add up inside a cluster.  prefetch / prefetch_bytes (optional, 16-byte aligned):
+// memory that a later kernel streams - the output projection's weights - which this kernel asks L2 for.
 extern "C" int fd_gemv_qkv_rope(const void* x, const void* w, const void* bias, int bias_f32, void* q_out,
                                 int M, int K, int n_splits, const float* cos_t, const float* sin_t, int table_len,
                                 const int* tok_row, const int* tok_pos, const int* row_slot, void* k_pool,
                                 void* v_pool, const int* block_table, int max_blocks, int num_blocks,
                                 int block_size, int n_q, int n_kv, int d, int write_kv, int* status,
-                                cudaStream_t stream) {
+                                const void* prefetch, unsigned long long prefetch_bytes, cudaStream_t stream) {
     if (M == 0) return 0;
+    FD_REQUIRE((uintptr_t)prefetch % 16 == 0, -2, "gemv_qkv_rope: the memory to prefetch must be 16-byte aligned");
     FD_REQUIRE(M >= 1 && M <= 64, -2, "gemv: %d rows of x; this kernel takes 1..64", M);
     FD_REQUIRE(K >= 32 && K % 32 == 0, -2, "gemv: K=%d must be a positive multiple of 32", K);
     FD_REQUIRE(d >= 16 && d % 16 == 0, -2, "gemv_qkv_rope: head size %d must be a multiple of 16", d);
@@ -287,6 +291,7 @@ extern "C" int fd_gemv_qkv_rope(const void* x, const void* w, const void* bias, 
     GemvParams p;
     p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = q_out;
     p.M = M; p.N = (n_q + 2 * n_kv) * d; p.K = K; p.n_splits = n_splits; p.mode = 4; p.bias_f32 = bias_f32;
+    p.pf_ptr = (const unsigned char*)prefetch; p.pf_bytes = prefetch ? prefetch_bytes : 0;
     RopeArgs ra;
     ra.cos_t = cos_t; ra.sin_t = sin_t; ra.tok_row = tok_row; ra.tok_pos = tok_pos; ra.row_slot = row_slot;
     ra.k_pool = (__nv_bfloat16*)k_pool; ra.v_pool = (__nv_bfloat16*)v_pool; ra.block_table = block_table;

@@ -74,7 +74,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_add_rmsnorm": [P, I, I, LL, P, I, P, I, F, P, I, P, I, I, P],
         "fd_silu_mul": [P, P, I, I, I, I, P],
         "fd_rope_append": [P, I, I, LL, P, I, P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
-        "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
+        "fd_gemv_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P, c_ulonglong, P],
         "fd_gemm_tc_supported": [I, I, I],
         "fd_gemm_tc_set_wide": [I],
         "fd_attn_prefill_set_form": [I],
@@ -238,10 +238,13 @@ def rope_append(qkv: torch.Tensor, q_out: torch.Tensor, cos: torch.Tensor, sin: 
 def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
                   cos: torch.Tensor, sin: torch.Tensor, tok_row: torch.Tensor, tok_pos: torch.Tensor,
                   row_slot: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
-                  n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor, n_splits: int = 1) -> None:
+                  n_q: int, n_kv: int, head_dim: int, write_kv: bool, status: torch.Tensor, n_splits: int = 1,
+                  prefetch: Optional[torch.Tensor] = None) -> None:
     """The q/k/v projection of a decode step (M <= 64 rows, bfloat16) with bias,
     rotary encoding and the append to the paged cache in its epilogue.  ``w``
-    and ``bias`` are in the paired row order (see ``rope_append``)."""
+    and ``bias`` are in the paired row order (see ``rope_append``).  ``prefetch``: a
+    tensor that a later kernel streams (the output projection's weights); the kernel
+    asks L2 for it once its own loads are through."""
     M, K = x.shape
     assert w.shape == ((n_q + 2 * n_kv) * head_dim, K) and q_out.shape == (M, n_q * head_dim)
     assert x.dtype == w.dtype == q_out.dtype == k_pool.dtype == torch.bfloat16
@@ -250,7 +253,8 @@ def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
                                   _ptr(q_out), M, K, n_splits, _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_row),
                                   _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                   block_table.shape[1], num_blocks, block_size, n_q, n_kv, head_dim, int(write_kv),
-                                  _ptr(status), _stream()))
+                                  _ptr(status), _ptr(prefetch),
+                                  prefetch.numel() * prefetch.element_size() if prefetch is not None else 0, _stream()))
 
 
 GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3

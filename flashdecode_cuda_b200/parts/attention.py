@@ -15,6 +15,7 @@ from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul, stream_gemm
 
 
 MAX_SPLITS = 32
+PREFETCH_BYTES = 16 << 20   # an output projection up to this size is asked for ahead by the decode q/k/v kernel
 FP32_SPLIT_LEN = 256      # keys per split of a decode step in float32
 
 
@@ -128,9 +129,10 @@ class GQAAttention(Mixer):
             splits = K.gemv_splits(T, self.w_qkv.shape[0], self.hidden_size, 4 * self.rt.sm_count)
         if splits >= 1:
             # decode: projection, bias, rotation and cache append in one kernel
+            # (and it asks L2 for the output projection's weights, which are read after the attention)
             K.gemv_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos, ctx.row_slot,
                             lc.k_pool, lc.v_pool, lc.group.table, self.n_q, self.n_kv, d, lc.writes, self.rt.status,
-                            splits)
+                            splits, prefetch=self.w_o if self.w_o.numel() * 2 <= PREFETCH_BYTES else None)
         elif self.paired and x.dtype == torch.bfloat16 and stream_gemm(T, self.w_qkv.shape[0], self.hidden_size):
             # larger decode batches and short prompts: the same fusion in the streaming tcgen05 kernel
             K.gemm_stream_qkv_rope(x, self.w_qkv, self.b_qkv, q, rope.cos, rope.sin, ctx.tok_row, ctx.tok_pos,

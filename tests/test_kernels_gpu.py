@@ -481,6 +481,19 @@ def test_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
         assert int(st.item()) == 0
         check(q_out, kp, vp, 6e-3)
         assert int((kp != 0).sum().item()) <= M * n_kv * d            # only this step's positions were written
+        # asked to fetch some other memory into L2 on the way (whole, and a size that is no multiple of a line or of
+        # the CTAs' shares): the same bits, and that memory untouched
+        for n_other in (5000, 8 + 13 * 1024):
+            other = torch.full((n_other,), 3.0, dtype=bf, device=DEV)
+            q2, kp2, vp2 = torch.zeros_like(q_out), torch.zeros_like(kp), torch.zeros_like(vp)
+            K.gemv_qkv_rope(x.to(DEV), wp, bp, q2, cos, sin, tok_row, tok_pos, row_slot, kp2, vp2, table.to(DEV),
+                            n_q, n_kv, d, True, st, splits, prefetch=other)
+            assert int(st.item()) == 0
+            assert torch.equal(q2, q_out) and torch.equal(kp2, kp) and torch.equal(vp2, vp)
+            assert bool((other == 3.0).all())
+    with pytest.raises(K.KernelError, match="16-byte"):
+        K.gemv_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp, table.to(DEV),
+                        n_q, n_kv, d, True, st, 1, prefetch=torch.zeros(64, dtype=bf, device=DEV)[1:])
     # the same fusion in the tcgen05 kernel that prompt steps use
     kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
     vp = torch.zeros_like(kp)
