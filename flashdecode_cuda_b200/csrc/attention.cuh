@@ -24,6 +24,10 @@ struct AttnParams {
     int n_q, n_kv, G, d;
     int QT, n_splits, split_len, window;
     float scale;
+    // decode steps on the tensor cores only: memory that a later kernel streams (the next part's first weights), or
+    // null; every CTA asks L2 for its share once its own keys and values are through
+    const unsigned char* pf_ptr;
+    unsigned long long pf_bytes;
 };
 
 // decode steps (one new token per row) on the tensor cores; returns 1 if it

@@ -361,6 +361,7 @@ __device__ __forceinline__ void attn_decode_item(const AttnParams& p, const int 
     }
 
     cp_async_wait<0>();
+    if (p.pf_bytes != 0 && tid == DM_THREADS - 1) l2_prefetch_share(p.pf_ptr, p.pf_bytes);
     // per-warp results to shared memory: O as float [16][D] in the warp's own staging area
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

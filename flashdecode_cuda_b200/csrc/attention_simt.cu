@@ -346,7 +346,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
                           const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
                           int max_q_len, int n_q, int n_kv, int d, float scale, int window,
                           int n_splits, int split_len, float* scratch, int* counters, int* status, int use_mma,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const void* prefetch = nullptr, unsigned long long prefetch_bytes = 0) {
     if (n_rows == 0 || T == 0) return 0;
     FD_REQUIRE(n_kv > 0 && n_q % n_kv == 0, -2, "attention: %d query heads are not a multiple of %d KV heads", n_q, n_kv);
     const int G = n_q / n_kv;
@@ -364,6 +364,7 @@ static int attention_impl(const void* q, const void* k_pool, const void* v_pool,
     FD_REQUIRE(n_rows <= 65535 && n_kv <= 65535, -2, "attention: batch of %d rows too large", n_rows);
 
     AttnParams p;
+    p.pf_ptr = (const unsigned char*)prefetch; p.pf_bytes = prefetch ? prefetch_bytes : 0;
     p.q = q; p.k_pool = k_pool; p.v_pool = v_pool; p.out = out;
     const size_t n_part = (size_t)T * n_q * n_splits;
     // accumulators first: they are stored as float4 and must stay 16-byte aligned
@@ -420,17 +421,20 @@ extern "C" int fd_attention_simt(const void* q, const void* k_pool, const void* 
 // The fastest kernel that takes the sizes: tensor cores where possible.  `counters`
 // (optional): n_rows * n_kv ints, all zero, which the decode kernel uses to let the last CTA of
 // a (sequence, KV head) merge the splits itself (it leaves them zero again); without them the
-// separate merge kernel runs.
+// separate merge kernel runs.  prefetch / prefetch_bytes (optional, 16-byte aligned): memory that a
+// later kernel streams, which the tensor-core decode kernel asks L2 for when its own reads are
+// through (the other kernels ignore it).
 extern "C" int fd_attention(const void* q, const void* k_pool, const void* v_pool, void* out, int dtype,
                             const int* block_table, int max_blocks, int num_blocks, int block_size,
                             const int* tok_row, const int* row_slot, const int* row_q_start,
                             const int* row_q_len, const int* row_ctx_len, int n_rows, int T,
                             int max_q_len, int n_q, int n_kv, int d, float scale, int window,
                             int n_splits, int split_len, float* scratch, int* counters, int* status,
-                            cudaStream_t stream) {
+                            const void* prefetch, unsigned long long prefetch_bytes, cudaStream_t stream) {
+    FD_REQUIRE((uintptr_t)prefetch % 16 == 0, -2, "attention: the memory to prefetch must be 16-byte aligned");
     return attention_impl(q, k_pool, v_pool, out, dtype, block_table, max_blocks, num_blocks, block_size, tok_row,
                           row_slot, row_q_start, row_q_len, row_ctx_len, n_rows, T, max_q_len, n_q, n_kv, d, scale,
-                          window, n_splits, split_len, scratch, counters, status, 1, stream);
+                          window, n_splits, split_len, scratch, counters, status, 1, stream, prefetch, prefetch_bytes);
 }
 
 // The same without the tcgen05 kernel: prompts go to the mma.sync kernel (head sizes other than 128 always

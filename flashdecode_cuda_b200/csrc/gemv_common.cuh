@@ -32,11 +32,12 @@ struct GemvParams {
     int mode;                    // 0: partial float [split, M, N]; 1: bf16 [M, N]; 2: float [M, N]; 3: gated bf16 [M, N / 2];
                                  // 4: q/k/v projection with rotary encoding and cache append (see RopeArgs)
     int bias_f32;
-    // Memory that a later kernel will stream (the output projection's weights, for the q/k/v projection), or null:
-    // each CTA asks L2 for its share once its own loads are through, so that HBM goes on delivering through this
-    // kernel's tail and the kernels after it.  Measured in the decode step of Qwen2.5-1.5B: - 1 % at batch 8, - 1.8 %
-    // at batch 1 for the 4.7 MB of the output projection; the same for the large matrices of the feed-forward made
-    // the step slower (their prefetch competes with the streams of the kernels that run meanwhile).
+    // Memory that a later kernel will stream (for the q/k/v projection the output projection's weights, which are
+    // read after the attention; for a block's last product the next block's first weights), or null: each CTA asks
+    // L2 for its share once its own loads are through, so that HBM goes on delivering through this kernel's tail and
+    // what follows.  It pays for what arrives before it is wanted: a few MB.  Measured in the decode step of
+    // Qwen2.5-1.5B: - 1 % at batch 8 and - 1.8 % at batch 1 for the 4.7 MB of the output projection; asking for all
+    // 27.5 MB of the down projection from the gate/up kernel made the step 1.2 % slower.
     const unsigned char* pf_ptr;
     unsigned long long pf_bytes;
 };

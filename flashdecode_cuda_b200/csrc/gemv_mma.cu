@@ -250,10 +250,13 @@ extern "C" int fd_gemv_splits(int M, int N, int K, int target_ctas, int allow_sp
 
 // mode 0: out = float partial sums [n_splits, M, N]; 1: bf16 [M, N]; 2: float [M, N] (both with
 // up to 8 splits added inside a cluster); 3: gated (rows of W in tiles of 8 gate + 8 up):
-// bf16 [M, N / 2], n_splits == 1.
+// bf16 [M, N / 2], n_splits == 1.  prefetch / prefetch_bytes (optional, 16-byte aligned): memory that a
+// later kernel streams, which this kernel asks L2 for once its own loads are through.
 extern "C" int fd_gemv(const void* x, const void* w, const void* bias, int bias_f32, void* out, int mode,
-                       int M, int N, int K, int n_splits, cudaStream_t stream) {
+                       int M, int N, int K, int n_splits, const void* prefetch, unsigned long long prefetch_bytes,
+                       cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
+    FD_REQUIRE((uintptr_t)prefetch % 16 == 0, -2, "gemv: the memory to prefetch must be 16-byte aligned");
     FD_REQUIRE(M >= 1 && M <= 64, -2, "gemv: %d rows of x; this kernel takes 1..64", M);
     FD_REQUIRE(K >= 32 && K % 32 == 0, -2, "gemv: K=%d must be a positive multiple of 32", K);
     FD_REQUIRE(n_splits >= 1 && (mode != 3 || n_splits == 1), -2, "gemv: the gated form cannot be split over K");
@@ -264,7 +267,7 @@ extern "C" int fd_gemv(const void* x, const void* w, const void* bias, int bias_
     GemvParams p;
     p.x = (const __nv_bfloat16*)x; p.w = (const __nv_bfloat16*)w; p.bias = bias; p.out = out;
     p.M = M; p.N = N; p.K = K; p.n_splits = n_splits; p.mode = mode; p.bias_f32 = bias_f32;
-    p.pf_ptr = nullptr; p.pf_bytes = 0;
+    p.pf_ptr = (const unsigned char*)prefetch; p.pf_bytes = prefetch ? prefetch_bytes : 0;
     RopeArgs ra = {};
     return run_gemv(p, ra, stream);
 }

@@ -73,6 +73,10 @@ class StepContext:
     h_ctx_len: List[int] = field(default_factory=list)
     # set for every schedule entry: whoever consumes the block's output takes float partial sums [parts, T, H]
     delta_parts_ok: bool = False
+    # set for every schedule entry, and by a block for each of its parts: the weights the step streams first after
+    # the part that runs now (``Part.first_weights`` of what follows), or None; a part may have its last kernel ask
+    # L2 for their beginning
+    upcoming: Optional[torch.Tensor] = None
 
 
 class _Staging:
@@ -380,6 +384,7 @@ class Model:
             # partial sums [parts, T, H] for a delta; a block hands that on to its last sub-layer
             nxt = self.blocks[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else self.final_norm
             ctx.delta_parts_ok = bool(getattr(nxt, "accepts_parts", False))
+            ctx.upcoming = (nxt if i + 1 < len(self.schedule) else self.head).first_weights()
             delta = self.blocks[run.layer].forward(ctx, resid, delta, caches[i])
             if self.trace is not None:
                 d = delta.float().sum(0) if delta.dim() == 3 else delta.float()

@@ -89,11 +89,11 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_gemm_stream_qkv_rope": [P, P, P, I, P, I, I, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
         "fd_tc_test_hook": [LL, I],
         "fd_gemv_splits": [I, I, I, I, I],
-        "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P],
+        "fd_gemv": [P, P, P, I, P, I, I, I, I, I, P, c_ulonglong, P],
         "fd_gemm_simt": [P, P, P, P, I, I, I, I, I, I, P],
         "fd_attn_simt_qt": [I],
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
-        "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
+        "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P, c_ulonglong, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
@@ -253,8 +253,7 @@ def gemv_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
                                   _ptr(q_out), M, K, n_splits, _ptr(cos), _ptr(sin), cos.shape[0], _ptr(tok_row),
                                   _ptr(tok_pos), _ptr(row_slot), _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                                   block_table.shape[1], num_blocks, block_size, n_q, n_kv, head_dim, int(write_kv),
-                                  _ptr(status), _ptr(prefetch),
-                                  prefetch.numel() * prefetch.element_size() if prefetch is not None else 0, _stream()))
+                                  _ptr(status), *_prefetch_args(prefetch, 1 << 62), _stream()))
 
 
 GEMV_PARTIAL, GEMV_BF16, GEMV_F32, GEMV_GATED = 0, 1, 2, 3
@@ -400,13 +399,21 @@ def gemv_splits(M: int, N: int, K: int, target_ctas: int, allow_split: bool = Tr
     return int(lib().fd_gemv_splits(M, N, K, target_ctas, int(allow_split)))
 
 
+def _prefetch_args(t: Optional[torch.Tensor], limit: int):
+    """(pointer, bytes) of the leading ``limit`` bytes of a tensor that a kernel is to ask L2 for."""
+    if t is None or limit <= 0:
+        return None, 0
+    return _ptr(t), min(int(limit), t.numel() * t.element_size()) & ~15
+
+
 def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
-         n_splits: int = 1) -> None:
+         n_splits: int = 1, prefetch: Optional[torch.Tensor] = None, prefetch_bytes: int = 1 << 62) -> None:
     """Weight-streaming product for M <= 64 rows (bfloat16): out = x w^T.
     mode GEMV_PARTIAL: out float32 [n_splits, M, N]; GEMV_BF16 / GEMV_F32: out
     [M, N] (+ bias), with ``n_splits`` <= 8 splits of K added inside a
     thread-block cluster; GEMV_GATED: w rows in tiles of 8 gate + 8 up, out
-    bfloat16 [M, N / 2] = silu(gate) * up."""
+    bfloat16 [M, N / 2] = silu(gate) * up.  ``prefetch``: a tensor that a later kernel
+    streams; the kernel asks L2 for its first ``prefetch_bytes`` once its own loads are through."""
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
@@ -414,7 +421,7 @@ def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: to
             GEMV_F32: (torch.float32, M * N), GEMV_GATED: (torch.bfloat16, M * N // 2)}[mode]
     assert out.dtype == want[0] and out.numel() == want[1], (out.dtype, out.shape, mode)
     _check(lib().fd_gemv(_ptr(x), _ptr(w), _ptr(bias), int(bias is not None and bias.dtype == torch.float32),
-                         _ptr(out), mode, M, N, K, n_splits, _stream()))
+                         _ptr(out), mode, M, N, K, n_splits, *_prefetch_args(prefetch, prefetch_bytes), _stream()))
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
@@ -442,7 +449,7 @@ def _counters(device, n: int) -> torch.Tensor:
 
 def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
                row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
-               scratch, status) -> None:
+               scratch, status, prefetch=None, prefetch_bytes=0) -> None:
     T = q.shape[0]
     num_blocks, _, block_size, _ = k_pool.shape
     assert q.dtype == k_pool.dtype == out.dtype
@@ -456,7 +463,10 @@ def _attention(fn_name, q, k_pool, v_pool, out, block_table, tok_row, row_slot, 
     if fn_name != "fd_attention_simt":
         fused = n_splits > 1 and max_q_len == 1 and q.dtype == torch.bfloat16
         args.append(_ptr(_counters(q.device, n_rows * n_kv)) if fused else None)
-    args += [_ptr(status), _stream()]
+    args.append(_ptr(status))
+    if fn_name == "fd_attention":
+        args += list(_prefetch_args(prefetch, prefetch_bytes))
+    args.append(_stream())
     _check(getattr(lib(), fn_name)(*args))
 
 
@@ -465,13 +475,16 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
               row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx_len: torch.Tensor,
               n_rows: int, max_q_len: int, n_q: int, n_kv: int, head_dim: int, scale: float,
               window: int = 0, n_splits: int = 1, split_len: int = 0,
-              scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> None:
+              scratch: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+              prefetch: Optional[torch.Tensor] = None, prefetch_bytes: int = 0) -> None:
     """Causal GQA attention of the step's tokens over the paged cache, by the
     fastest kernel that takes the sizes (tensor cores for bfloat16 decode steps
-    with head size 64 or 128; the CUDA-core kernel otherwise)."""
+    with head size 64 or 128; the CUDA-core kernel otherwise).  ``prefetch``: a
+    tensor that a later kernel streams; the tensor-core decode kernel asks L2 for its
+    first ``prefetch_bytes`` when its own reads are through (the other kernels do not)."""
     _attention("fd_attention", q, k_pool, v_pool, out, block_table, tok_row, row_slot, row_q_start, row_q_len,
                row_ctx_len, n_rows, max_q_len, n_q, n_kv, head_dim, scale, window, n_splits, split_len,
-               scratch, status)
+               scratch, status, prefetch, prefetch_bytes)
 
 
 def attention_mma_sync(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,

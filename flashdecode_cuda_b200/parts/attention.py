@@ -11,7 +11,7 @@ from .. import kernels as K
 from ..registry import register_part
 from ..weights.spec import TensorSpec
 from .base import KVRequest, LayerCache, Mixer, Runtime
-from .linear import GEMV_MAX_ROWS, fused_prompt_gemm, matmul, stream_gemm
+from .linear import GEMV_MAX_ROWS, UPCOMING_BYTES, fused_prompt_gemm, matmul, stream_gemm
 
 
 MAX_SPLITS = 32
@@ -119,6 +119,9 @@ class GQAAttention(Mixer):
         return n
 
     # --- a step ----------------------------------------------------------
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_qkv
+
     def forward(self, ctx, x: torch.Tensor, lc: LayerCache) -> torch.Tensor:
         T, d = ctx.T, self.d
         ws = ctx.ws
@@ -162,9 +165,12 @@ class GQAAttention(Mixer):
             if n_splits > 1:
                 scratch = ws.get("attn_scratch", (K.attention_scratch_floats(T, self.n_q, d, n_splits),),
                                  torch.float32)
+        # a small decode step: when its keys and values are through, the attention kernel asks L2 for the beginning of
+        # what the step streams after this part (the output projection's weights are in L2 already, see above)
+        ahead = ctx.upcoming if ctx.max_q_len == 1 and T <= GEMV_MAX_ROWS and x.dtype == torch.bfloat16 else None
         K.attention(q, lc.k_pool, lc.v_pool, attn, lc.group.table, ctx.tok_row, ctx.row_slot,
                          ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.n_rows, ctx.max_q_len,
                          self.n_q, self.n_kv, d, self.scale, self.window or 0, n_splits, split_len, scratch,
-                         self.rt.status)
+                         self.rt.status, prefetch=ahead, prefetch_bytes=UPCOMING_BYTES)
         out = ws.get("mixer_out", (T, self.hidden_size), x.dtype)
         return matmul(attn, self.w_o, None, out, target_ctas=4 * self.rt.sm_count, status=self.rt.status)

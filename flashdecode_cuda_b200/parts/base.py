@@ -96,6 +96,11 @@ class Part:
         """Bytes of weights one step has to read (for the roofline model)."""
         return 0
 
+    def first_weights(self) -> Optional[torch.Tensor]:
+        """The weights a decode step of this part streams first, or None.  Whoever runs the parts offers them
+        to the part that runs before (``ctx.upcoming``), whose last kernel may ask L2 for their beginning."""
+        return None
+
 
 class Embedding(Part):
     kind = "embedding"

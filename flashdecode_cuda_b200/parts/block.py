@@ -27,6 +27,9 @@ class PreNormBlock(Block):
     def parts(self):
         return [self.norm1, self.mixer, self.norm2, self.feed_forward]
 
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.mixer.first_weights()
+
     @property
     def accepts_parts(self) -> bool:
         """The incoming delta goes straight to norm1."""
@@ -34,9 +37,12 @@ class PreNormBlock(Block):
 
     def forward(self, ctx, resid: torch.Tensor, delta: Optional[torch.Tensor], lc: LayerCache) -> torch.Tensor:
         xn = ctx.ws.get("normed", tuple(resid.shape), ctx.rt.dtype)
+        after_block = ctx.upcoming                       # what the step streams after this block (set by the model)
         self.norm1.forward(ctx, delta, resid, xn)
+        ctx.upcoming = self.feed_forward.first_weights()
         d1 = self.mixer.forward(ctx, xn, lc)
         self.norm2.forward(ctx, d1, resid, xn)
+        ctx.upcoming = after_block
         # float partial sums only if whoever adds this block's output has said it takes them
         if ctx.delta_parts_ok and getattr(self.feed_forward, "offers_parts", False):
             return self.feed_forward.forward(ctx, xn, parts_ok=True)

@@ -32,6 +32,9 @@ class LinearHead(Head):
         self.rt = rt
         self.weight = tensors[self.tied_to or self.name]
 
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.weight
+
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 

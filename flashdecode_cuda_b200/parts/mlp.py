@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -48,6 +48,9 @@ class SwiGLU(FeedForward):
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size()
 
+    def first_weights(self) -> Optional[torch.Tensor]:
+        return self.w_gate_up
+
     def forward(self, ctx, x: torch.Tensor, parts_ok: bool = False) -> torch.Tensor:
         """delta [T, H]; with ``parts_ok`` (the caller's consumer adds partial sums up) a decode step's down
         projection may come back as float32 [parts, T, H] instead."""
@@ -68,4 +71,5 @@ class SwiGLU(FeedForward):
         parts = None
         if parts_ok and T <= GEMV_MAX_ROWS:
             parts = ws.get("ffn_out_parts", (MAX_PARTS, T, self.hidden_size), torch.float32)
-        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, parts=parts, status=self.rt.status)
+        return matmul(act, self.w_down, None, out, target_ctas=4 * self.rt.sm_count, parts=parts, status=self.rt.status,
+                      upcoming=ctx.upcoming)
