@@ -115,6 +115,34 @@ def test_long_decoding(engines, folders, name, dtype):
     eng.model.check_status()
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_asking_l2_for_what_comes_next_changes_no_bit(engines, folders, name, monkeypatch):
+    """Decode steps hand ``ctx.upcoming`` (the weights the step streams next) to their kernels, which ask L2
+    for its beginning.  With that switched off, with the usual size and with a size that is no multiple of
+    anything, the logits are the same bits."""
+    from flashdecode_cuda_b200.parts import attention as A, linear as L
+    eng = engines[(name, "bfloat16")]
+    reqs = prompts_for(TINY[name]["vocab_size"], [40, 23, 31], seed=9)
+    outs = []
+    for nbytes, o_bytes in ((0, 0), (L.UPCOMING_BYTES, A.PREFETCH_BYTES), (1000, 1 << 30)):
+        monkeypatch.setattr(A, "UPCOMING_BYTES", nbytes)
+        monkeypatch.setattr(L, "UPCOMING_BYTES", nbytes)
+        monkeypatch.setattr(A, "PREFETCH_BYTES", o_bytes)
+        cache = eng.model.new_cache(max_tokens=256, block_size=16)
+        slots = [cache.admit() for _ in reqs]
+        eng.model.step(cache, slots, [r[:20] for r in reqs], None)
+        got = []
+        for i in range(20, 23):
+            got.append(eng.model.step(cache, slots, [[r[i]] for r in reqs], "last").clone())
+        outs.append(torch.stack(got))
+        for s_ in slots:
+            cache.release(s_)
+    eng.model.check_status()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    for j, r in enumerate(reqs):
+        assert rel_err(outs[1][2][j], oracle_logits(folders[name], r)[22]) < TOL["bfloat16"]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", CONFIGS)
 def test_first_tokens_of_a_sequence(engines, folders, name, dtype):
