@@ -36,8 +36,13 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[Tuple, torch.Tensor] = {}      # (name, dtype, shape) -> view; dropped when its buffer grows
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        key = (name, dtype, shape)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -45,7 +50,13 @@ class Workspace:
         if buf is None or buf.numel() < n:
             buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[(name, dtype)] = buf
-        return buf[:n].view(shape)
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[k]
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = buf[:n].view(shape)
+        self._views[key] = view
+        return view
 
 
 @dataclass

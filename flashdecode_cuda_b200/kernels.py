@@ -121,7 +121,15 @@ def launch_count() -> int:
     return int(lib().fd_launch_count())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  torch's own accessor for the raw handle costs a fraction of a microsecond;
+    ``torch.cuda.current_stream()`` builds a Stream object each time (about 5 us), which in a prompt step of some
+    250 launches was a sixth of the host's time."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
