@@ -408,10 +408,11 @@ def gemv_splits(M: int, N: int, K: int, target_ctas: int, allow_split: bool = Tr
 
 
 def _prefetch_args(t: Optional[torch.Tensor], limit: int):
-    """(pointer, bytes) of the leading ``limit`` bytes of a tensor that a kernel is to ask L2 for."""
-    if t is None or limit <= 0:
+    """(pointer, bytes) of the leading ``limit`` bytes of a tensor that a kernel is to ask L2 for.  It is a hint:
+    a tensor the kernels cannot take it from (not on the device, not contiguous, not 16-byte aligned) is passed over."""
+    if t is None or limit <= 0 or not t.is_cuda or not t.is_contiguous() or t.data_ptr() % 16 != 0:
         return None, 0
-    return _ptr(t), min(int(limit), t.numel() * t.element_size()) & ~15
+    return t.data_ptr(), min(int(limit), t.numel() * t.element_size()) & ~15
 
 
 def gemv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,

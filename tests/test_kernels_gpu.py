@@ -491,9 +491,10 @@ def test_projection_with_rotary_epilogue(n_q, n_kv, d, bs, Kd, M):
             assert int(st.item()) == 0
             assert torch.equal(q2, q_out) and torch.equal(kp2, kp) and torch.equal(vp2, vp)
             assert bool((other == 3.0).all())
-    with pytest.raises(K.KernelError, match="16-byte"):
-        K.gemv_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp, table.to(DEV),
-                        n_q, n_kv, d, True, st, 1, prefetch=torch.zeros(64, dtype=bf, device=DEV)[1:])
+    # a hint the kernel cannot take (not 16-byte aligned) is passed over, not an error
+    K.gemv_qkv_rope(x.to(DEV), wp, bp, q_out, cos, sin, tok_row, tok_pos, row_slot, kp, vp, table.to(DEV),
+                    n_q, n_kv, d, True, st, 1, prefetch=torch.zeros(64, dtype=bf, device=DEV)[1:])
+    assert int(st.item()) == 0
     # the same fusion in the tcgen05 kernel that prompt steps use
     kp = torch.zeros(total, n_kv, bs, d, dtype=bf, device=DEV)
     vp = torch.zeros_like(kp)
