@@ -119,11 +119,13 @@ __global__ void add_rmsnorm_row_kernel(const __nv_bfloat16* __restrict__ delta, 
     }
 }
 
-// The row form for a delta that is float partial sums [n_parts <= 4][rows][H] of a product split
+// The row form for a delta that is float partial sums [n_parts <= MAXP][rows][H] of a product split
 // over K: every part's loads are issued together with the residual's, and the parts are added in
-// order.
-template <typename TW>
-__global__ void add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, int n_parts, size_t part_stride,
+// order.  MAXP 4, or 8 for rows of up to 4096 elements (512 threads: eight parts' loads in flight take registers
+// that a CTA of 1024 threads does not have).
+template <typename TW, int MAXP>
+__global__ void __launch_bounds__(MAXP > 4 ? 512 : 1024)
+add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, int n_parts, size_t part_stride,
                                              float* __restrict__ resid, int write_resid, const TW* __restrict__ w, float eps,
                                              __nv_bfloat16* __restrict__ out, const int* __restrict__ rows, int H) {
     pdl_launch_dependents();
@@ -137,9 +139,9 @@ __global__ void add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, in
     if (i < H) {
         float* rrow = resid + (size_t)r * H + i;
         const float4 r0 = *reinterpret_cast<const float4*>(rrow), r1 = *reinterpret_cast<const float4*>(rrow + 4);
-        float4 d[4][2];
+        float4 d[MAXP][2];
 #pragma unroll
-        for (int pt = 0; pt < 4; ++pt)
+        for (int pt = 0; pt < MAXP; ++pt)
             if (pt < n_parts) {
                 const float* prow = parts + pt * part_stride + (size_t)r * H + i;
                 d[pt][0] = *reinterpret_cast<const float4*>(prow);
@@ -158,7 +160,7 @@ __global__ void add_rmsnorm_row_parts_kernel(const float* __restrict__ parts, in
         x[0] = r0.x; x[1] = r0.y; x[2] = r0.z; x[3] = r0.w; x[4] = r1.x; x[5] = r1.y; x[6] = r1.z; x[7] = r1.w;
         // the residual, then the parts in order: the order of the general kernel
 #pragma unroll
-        for (int pt = 0; pt < 4; ++pt)
+        for (int pt = 0; pt < MAXP; ++pt)
             if (pt < n_parts) {
                 x[0] += d[pt][0].x; x[1] += d[pt][0].y; x[2] += d[pt][0].z; x[3] += d[pt][0].w;
                 x[4] += d[pt][1].x; x[5] += d[pt][1].y; x[6] += d[pt][1].z; x[7] += d[pt][1].w;
@@ -358,13 +360,21 @@ extern "C" int fd_add_rmsnorm(const void* delta, int delta_dtype, int n_parts, l
         return launch("add_rmsnorm", add_rmsnorm_row_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
                       (const bf16*)delta, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
     }
-    if (out_dtype == 1 && delta != nullptr && delta_dtype == 0 && n_parts <= 4 && H % 8 == 0 && H <= 8192 && ps % 4 == 0 &&
+    if (out_dtype == 1 && delta != nullptr && delta_dtype == 0 && (n_parts <= 4 || (n_parts <= 8 && H <= 4096)) && H % 8 == 0 &&
+        H <= 8192 && ps % 4 == 0 &&
         (uintptr_t)resid % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)delta % 16 == 0) {
         const int threads = ((H / 8 + 31) / 32) * 32;
+        if (n_parts <= 4) {
+            if (w_dtype == 0)
+                return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<float, 4>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+                              (const float*)delta, n_parts, ps, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
+            return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<bf16, 4>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+                          (const float*)delta, n_parts, ps, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
+        }
         if (w_dtype == 0)
-            return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<float>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+            return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<float, 8>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
                           (const float*)delta, n_parts, ps, resid, write_resid, (const float*)weight, eps, (bf16*)out, rows, H);
-        return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
+        return launch("add_rmsnorm", add_rmsnorm_row_parts_kernel<bf16, 8>, dim3(n_out), dim3(threads), 0, stream, dim3(1, 1, 1),
                       (const float*)delta, n_parts, ps, resid, write_resid, (const bf16*)weight, eps, (bf16*)out, rows, H);
     }
     if (delta_dtype == 0 && out_dtype == 0)

@@ -198,16 +198,33 @@ static int launch_gemv(const GemvParams& p, const RopeArgs& ra, cudaStream_t str
 
 // Measured on B200 (graph-timed, weights beyond L2): wide matrices stream best with 32 rows
 // per CTA (4 or more CTAs per SM), narrow ones with 16 rows per CTA plus a split of K.
-static int pick_wk(int N) { return N >= 8192 ? 4 : 8; }
+static int gemv_slots() {            // 8-warp CTAs of at most 64 registers that the GPU holds at once
+    static int slots = 0;
+    if (slots == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        slots = 4 * sms;
+    }
+    return slots;
+}
+// 32 rows per CTA (4 warps slicing K) for wide matrices, and for narrower ones whose 16-row CTAs times their splits
+// of K would not fit the GPU at once: a second, nearly empty wave cost a fifth of the kernel's time (down projection
+// of Qwen2.5-7B, 3584 x 18944: 672 CTAs of 16 rows 30.1 us, 560 CTAs of 32 rows 23.8 us; o projection of
+// Qwen2.5-14B 16.8 -> 13.3 us).
+static int pick_wk(int N, int n_splits) {
+    if (N >= 8192) return 4;
+    return (long long)((N + 15) / 16) * n_splits > gemv_slots() ? 4 : 8;
+}
 
 template <int NT, int UNROLL>
 static int launch_gemv_wk(const GemvParams& p, const RopeArgs& ra, cudaStream_t stream) {
     if constexpr (NT <= 2) {
         // narrow and not split across CTAs: 16 warps share the 16 rows of a CTA (measured 4.2 us against
         // 5.2 us with 8 warps for the q/k/v and o projections of Qwen2.5-1.5B)
-        if (p.n_splits == 1 && pick_wk(p.N) == 8) return launch_gemv<NT, 16, (UNROLL > 4 ? 4 : UNROLL), 16>(p, ra, stream);
+        if (p.n_splits == 1 && pick_wk(p.N, 1) == 8) return launch_gemv<NT, 16, (UNROLL > 4 ? 4 : UNROLL), 16>(p, ra, stream);
     }
-    if (pick_wk(p.N) == 4) return launch_gemv<NT, 4, UNROLL>(p, ra, stream);
+    if (pick_wk(p.N, p.n_splits) == 4) return launch_gemv<NT, 4, UNROLL>(p, ra, stream);
     return launch_gemv<NT, 8, UNROLL>(p, ra, stream);
 }
 
@@ -235,17 +252,28 @@ using namespace fd;
 extern "C" int fd_gemv_splits(int M, int N, int K, int target_ctas, int allow_split) {
     if (M < 1 || M > 64 || K < 32 || K % 32 != 0 || N < 1) return 0;
     if (!allow_split) return 1;
-    const int rows = 16 * (GV_WARPS / pick_wk(N));
-    const int row_blocks = (N + rows - 1) / rows;
-    int want = (target_ctas + row_blocks / 2) / row_blocks;
     const int chunks = K / 32;
     // A split across CTAs costs a cluster launch and two cluster barriers (about 3 us measured on
-    // B200): worth it only while every warp of a CTA still walks 8 or more chunks.
-    if (want > chunks / (8 * 8)) want = chunks / (8 * 8);
-    if (want > 8) want = 8;                               // the most CTAs a portable cluster holds
-    if (want < 1) want = 1;
-    const int per = ((chunks + want - 1) / want) * 32;    // k per split, multiple of 32
-    return (K + per - 1) / per;
+    // B200), or partial sums for a consumer to add: worth it only while every warp of a CTA still walks 8 or more chunks.
+    int cap = chunks / (8 * 8);
+    if (cap > 8) cap = 8;                                 // the most CTAs a portable cluster holds
+    if (cap < 1) cap = 1;
+    auto splits_for = [&](int want) {                     // the splits that k ranges of a multiple of 32 give
+        if (want > cap) want = cap;
+        if (want < 1) want = 1;
+        const int per = ((chunks + want - 1) / want) * 32;
+        return (K + per - 1) / per;
+    };
+    const int rows = 16 * (GV_WARPS / (N >= 8192 ? 4 : 8));
+    const int row_blocks = (N + rows - 1) / rows;
+    int s = splits_for((target_ctas + row_blocks / 2) / row_blocks);
+    // 16-row CTAs that would spill into a second wave: 32-row CTAs instead (see pick_wk), as many as fit at once
+    if (N < 8192 && (long long)row_blocks * s > gemv_slots()) {
+        const int rb4 = (N + 31) / 32;
+        const int s4 = splits_for(gemv_slots() / rb4);
+        if ((long long)rb4 * s4 <= gemv_slots() && (long long)row_blocks * s4 > gemv_slots()) s = s4;
+    }
+    return s;
 }
 
 // mode 0: out = float partial sums [n_splits, M, N]; 1: bf16 [M, N]; 2: float [M, N] (both with

@@ -29,7 +29,7 @@ PROMPT_GEMM = "auto"
 # Up to this many rows the weight-streaming kernel beats the library product (measured on
 # B200 at the sizes of Qwen2.5-1.5B); above it the rows of x no longer fit the registers' reach.
 GEMV_MAX_ROWS = 16
-MAX_PARTS = 4           # most partial sums the norm's fast kernel adds up
+MAX_PARTS = 8           # most partial sums the norm's fast kernel adds up
 # Up to this many rows (and above GEMV_MAX_ROWS) the streaming tcgen05 kernel takes the product with
 # its fused epilogues: the rows of x are the N side of its MMAs, so nothing is padded to a 128-row tile.
 STREAM_MAX_ROWS = 128

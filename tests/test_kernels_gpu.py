@@ -92,7 +92,8 @@ def test_add_rmsnorm_partial_sums():
     assert rel(out, P.rmsnorm(x, w.double(), 1e-6)) < 1e-5
 
 
-@pytest.mark.parametrize("n_parts,rows,H", [(1, 8, 1536), (2, 3, 200), (4, 16, 8192), (5, 2, 1536), (3, 4, 1537), (4, 5, 8200)])
+@pytest.mark.parametrize("n_parts,rows,H", [(1, 8, 1536), (2, 3, 200), (4, 16, 8192), (5, 2, 1536), (3, 4, 1537), (4, 5, 8200),
+                                            (8, 8, 3584), (7, 3, 4096), (6, 4, 5120), (8, 2, 8192)])
 def test_add_rmsnorm_partial_sums_to_bfloat16(n_parts, rows, H):
     """Float partial sums of a split product, bfloat16 output: the row kernel for up to four parts
     and widths that are multiples of 8 up to 8192, the general kernel otherwise; only chosen rows too."""
