@@ -159,9 +159,11 @@ def plan_trials(context: int, longest_prompt: int, steps: int, warmup: int, tria
 
 
 def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: int, e2e: bool,
-               prompt_range=None, profile: bool = False, block_size: int = BLOCK_SIZE, trials: int = TRIALS):
+               prompt_range=None, profile: bool = False, block_size: int = BLOCK_SIZE, trials: int = TRIALS, decoder=None):
     """Prefill ragged prompts, decode untimed until ``trials * steps + warmup`` steps are left before the
-    longest sequence reaches ``context``, then time ``trials`` runs of ``steps`` steps each."""
+    longest sequence reaches ``context``, then time ``trials`` runs of ``steps`` steps each.  ``decoder``: run in this
+    decoder's (empty) cache with the graphs it has captured already, instead of a new cache and new captures; the
+    device-timed run returns its decoder as ``out["decoder"]``."""
     import torch
     from flashdecode_cuda_b200 import kernels as K
     from flashdecode_cuda_b200.engine.decode import GraphDecoder
@@ -170,7 +172,11 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
     lo, hi = prompt_range or (context // 4, context // 2)
     prompts = ragged_prompts(batch, lo, hi, vocab, seed)
     longest = max(len(p) for p in prompts)
-    cache = model.new_cache(batch_size=batch, max_len=context, block_size=block_size)
+    if decoder is not None:
+        cache = decoder.cache
+        engine.use_decoder(decoder)
+    else:
+        cache = model.new_cache(batch_size=batch, max_len=context, block_size=block_size)
     out = {}
     if e2e:
         # the public entry point: host token ids in, host token ids out, every step
@@ -200,7 +206,7 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
     slots = [cache.admit() for _ in prompts]
     logits = model.step(cache, slots, prompts, "last")
     first = engine.sampler.sample(logits).tolist()
-    dec = GraphDecoder(model, cache)
+    dec = decoder if decoder is not None else GraphDecoder(model, cache)
     dec.run(slots, first)
     n_fast = context - longest - 1 - trials * steps - warmup
     for _ in range(n_fast + warmup):
@@ -231,6 +237,7 @@ def decode_run(engine, batch: int, context: int, steps: int, warmup: int, seed: 
                trials_ms=[round(t, 4) for t in times], spread=(max(times) - min(times)) / min(times))
     for s in slots:
         cache.release(s)
+    out["decoder"] = dec
     return out
 
 
@@ -510,8 +517,11 @@ def main() -> int:
                           trials=1 if args.profile_range else TRIALS)
     points, prefill, e2e = {}, None, None
     if not args.no_points:
+        # the end-to-end run goes through the same cache and the decode graphs captured for it
         e2e = decode_run(engine, args.batch, args.context, args.steps, warmup, args.seed, e2e=True,
-                         block_size=args.block_size)
+                         block_size=args.block_size, decoder=main_run["decoder"])
+    del main_run["decoder"]
+    if not args.no_points:
         for b in (1, 64):
             r = decode_run(engine, b, args.context, args.steps, warmup, args.seed + b, e2e=False,
                            block_size=args.block_size)

@@ -62,6 +62,16 @@ extern "C" int fd_set_pdl(int on) {
 
 // One asynchronous copy from pinned host memory to the device on the given stream (the per-step index
 // array of a decode step; a plain call costs a fraction of a tensor-library copy on the host).
+// One copy from the device into pinned host memory on the given stream, and the wait for it: what a decode step's
+// tokens cost on their way to the host (one call instead of a tensor-library copy and a stream object's synchronize).
+extern "C" int fd_copy_d2h_sync(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+    if (bytes <= 0) return 0;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fd::fail(-100, "copy to the host failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 extern "C" int fd_copy_h2d_async(void* dst, const void* src, long long bytes, cudaStream_t stream) {
     if (bytes <= 0) return 0;
     cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream);

@@ -94,6 +94,14 @@ class Engine(Backend):
             self._graph_decoder = GraphDecoder(self.model, self.cache)
         return self._graph_decoder
 
+    def use_decoder(self, decoder: GraphDecoder) -> None:
+        """Decode steps over ``decoder.cache`` go through this decoder from now on, with the graphs it has captured
+        already (a graph is tied to its cache's tensors; capturing one costs tens of milliseconds).  Pass that cache to
+        ``generate`` / ``stream``."""
+        if decoder.model is not self.model:
+            raise ValueError("the decoder belongs to another model")
+        self._graph_decoder = decoder
+
     # -- generation ---------------------------------------------------------
     def _requests(self, input_ids, max_new_tokens, temperature, stop_token_ids) -> List[Request]:
         if isinstance(input_ids, torch.Tensor):

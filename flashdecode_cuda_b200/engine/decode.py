@@ -27,7 +27,7 @@ from ..cache.paged import PagedCache
 from .model import Model, StepContext, Workspace
 
 BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
-KV_BOUND_STEP = 1024
+KV_BOUND_MIN = 1024      # the length bound of a graph is a power of two from here on (or the cache's longest sequence)
 
 
 def bucket_of(n: int) -> int:
@@ -65,13 +65,20 @@ class GraphDecoder:
         self.last_n = 0
         self.launches_per_step = 0
         self._host_out: Optional[torch.Tensor] = None
+        self._host_view: Optional[np.ndarray] = None
         # (graph, slots, the cache's lengths_version): the next step's slots and lengths are in that graph's index
         # array already; void as soon as any sequence of the cache has started, ended or grown since
         self._ahead: Optional[Tuple] = None
 
     # ------------------------------------------------------------------
     def _key(self, n: int, longest: int, greedy: bool, seed: int) -> Tuple:
-        bound = min(-(-longest // KV_BOUND_STEP) * KV_BOUND_STEP, self.cache.max_len)
+        # powers of two: a sequence that grows from 1,000 to 4,000 tokens passes three bounds, not four, and a process
+        # that captures fewer graphs stays clear of the slower replay that set in after the fourth capture (the same
+        # graph 1.25 or 1.33 ms a step; which one changed with captures and large allocations, nothing else)
+        bound = KV_BOUND_MIN
+        while bound < longest:
+            bound *= 2
+        bound = min(bound, self.cache.max_len)
         return (bucket_of(n), bound, greedy, seed if not greedy else 0)
 
     def _prepare(self, g: _Graph, key: Tuple, slots: Sequence[int], tokens: Sequence[int]) -> StepContext:
@@ -210,6 +217,9 @@ class GraphDecoder:
         src = self.last.sampled
         if self._host_out is None or self._host_out.numel() < src.numel():
             self._host_out = torch.empty(max(src.numel(), 256), dtype=torch.int32).pin_memory()
-        self._host_out[:src.numel()].copy_(src, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._host_out[:n].tolist()
+            self._host_view = self._host_out.numpy()
+        if src.is_cuda:
+            K.copy_d2h_sync(self._host_out, src, n)
+        else:
+            self._host_out[:n].copy_(src[:n])
+        return self._host_view[:n].tolist()

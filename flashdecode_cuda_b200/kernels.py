@@ -97,6 +97,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
         "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
+        "fd_copy_d2h_sync": [P, P, LL, P],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)
@@ -166,6 +167,13 @@ def set_pdl(on: bool) -> None:
 def copy_h2d_async(dst: torch.Tensor, src_pinned: torch.Tensor, n_elements: int) -> None:
     """dst[:n] <- src[:n] from pinned host memory, asynchronously on the current stream."""
     rc = lib().fd_copy_h2d_async(dst.data_ptr(), src_pinned.data_ptr(), n_elements * dst.element_size(), _stream())
+    if rc != 0:
+        raise KernelError(lib().fd_last_error().decode())
+
+
+def copy_d2h_sync(dst_pinned: torch.Tensor, src: torch.Tensor, n_elements: int) -> None:
+    """dst[:n] <- src[:n] into pinned host memory on the current stream, waited for."""
+    rc = lib().fd_copy_d2h_sync(dst_pinned.data_ptr(), src.data_ptr(), n_elements * src.element_size(), _stream())
     if rc != 0:
         raise KernelError(lib().fd_last_error().decode())
 

@@ -127,6 +127,38 @@ def test_new_sequences_in_the_same_slots_of_the_same_graph(folders):
     model.check_status()
 
 
+def test_engine_uses_a_decoder_it_is_given(folders):
+    """``Engine.use_decoder``: generation over a decoder's cache goes through that decoder and the graphs it has
+    captured - none is captured anew - and a decoder's length bounds are powers of two."""
+    from flashdecode_cuda_b200.engine.decode import GraphDecoder, KV_BOUND_MIN
+    eng = fd.load(folders["B"], device="cuda", dtype="float32")
+    raw, w = raw_config(folders["B"]), weights_of(folders["B"])
+    model = eng.model
+    cache = model.new_cache(batch_size=2, max_len=128, block_size=8)
+    dec = GraphDecoder(model, cache)
+    assert dec._key(2, 5, True, 0)[1] == min(KV_BOUND_MIN, cache.max_len)
+    import types
+    probe = GraphDecoder(model, cache)
+    probe.cache = types.SimpleNamespace(max_len=5000)        # _key reads nothing else of the cache
+    bounds = [probe._key(1, n, True, 0)[1] for n in (1, 1024, 1025, 2048, 2049, 4096, 4097, 5000)]
+    assert bounds == [1024, 1024, 2048, 2048, 4096, 4096, 5000, 5000]
+    prompts = prompts_for(raw["vocab_size"], [9, 4], seed=21)
+    slots = [cache.admit() for _ in prompts]
+    toks = eng.sampler.sample(model.step(cache, slots, prompts, "last")).tolist()
+    dec.run(slots, toks)                                     # captures the graph of this bucket and bound
+    for s_ in slots:
+        cache.release(s_)
+    captured = dict(dec.graphs)
+    eng.use_decoder(dec)
+    got = [r.tokens for r in eng.generate(prompts, 6, cache)]
+    assert got == [P.generate(raw, w, p, 6) for p in prompts]
+    assert eng._decoder() is dec and dec.graphs == captured      # the same graphs, none added
+    other = fd.load(folders["C"], device="cuda", dtype="float32")
+    with pytest.raises(ValueError, match="another model"):
+        other.use_decoder(dec)
+    model.check_status()
+
+
 def test_command_line(folders, tmp_path):
     cmd = [sys.executable, "-m", "flashdecode_cuda_b200", "generate", "--model", str(folders["B"]),
            "--prompt-ids", "5,6,7", "--prompt-ids", "300,2", "--max-new-tokens", "5", "--dtype", "float32",
