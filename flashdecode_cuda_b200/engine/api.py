@@ -51,6 +51,7 @@ class Engine(Backend):
         # decode steps replay captured CUDA graphs unless a part decides on the host
         self.use_graphs = model.device.type == "cuda" and model.graph_safe
         self._graph_decoder: Optional[GraphDecoder] = None
+        self._own_cache: Optional[PagedCache] = None       # the cache made by a call that was given none
 
     # -- caches -----------------------------------------------------------
     def new_paged_cache(self, batch_size: int, max_len: int, block_size: int = DEFAULT_BLOCK_SIZE,
@@ -122,7 +123,14 @@ class Engine(Backend):
         max_batch = max_batch or min(len(requests), 64)
         if cache is None:
             longest = max(len(r.prompt) + r.max_new_tokens for r in requests)
-            cache = self.new_paged_cache(max_batch, longest, block_size)
+            own = self._own_cache
+            # the cache this engine made for an earlier call serves again if it is large enough and empty: no new
+            # allocation, and the decode graphs captured over it are used again instead of being captured anew
+            if (own is not None and own.block_size == block_size and own.max_slots >= max_batch
+                    and own.max_len >= longest and not own.active_slots()):
+                cache = own
+            else:
+                cache = self._own_cache = self.new_paged_cache(max_batch, longest, block_size)
         self.cache = cache
         return max_batch
 

@@ -159,6 +159,25 @@ def test_engine_uses_a_decoder_it_is_given(folders):
     model.check_status()
 
 
+def test_engine_keeps_its_cache_and_graphs_between_calls(folders):
+    """A call that is given no cache makes one; the next call uses it again if it is large enough and empty, and with
+    it the decode graphs captured over it; a call that needs more gets a new one."""
+    eng = fd.load(folders["B"], device="cuda", dtype="float32")
+    raw, w = raw_config(folders["B"]), weights_of(folders["B"])
+    first = prompts_for(raw["vocab_size"], [9, 4, 12], seed=31)
+    second = prompts_for(raw["vocab_size"], [5, 7], seed=32)
+    assert [r.tokens for r in eng.generate(first, 8)] == [P.generate(raw, w, p, 8) for p in first]
+    cache, dec = eng.cache, eng._decoder()
+    graphs = dict(dec.graphs)
+    assert graphs
+    assert [r.tokens for r in eng.generate(second, 6)] == [P.generate(raw, w, p, 6) for p in second]
+    assert eng.cache is cache and eng._decoder() is dec and not cache.active_slots()
+    longer = prompts_for(raw["vocab_size"], [30], seed=33)
+    assert [r.tokens for r in eng.generate(longer, 20)] == [P.generate(raw, w, p, 20) for p in longer]
+    assert eng.cache is not cache                      # 50 tokens did not fit the first cache's longest sequence
+    eng.model.check_status()
+
+
 def test_command_line(folders, tmp_path):
     cmd = [sys.executable, "-m", "flashdecode_cuda_b200", "generate", "--model", str(folders["B"]),
            "--prompt-ids", "5,6,7", "--prompt-ids", "300,2", "--max-new-tokens", "5", "--dtype", "float32",
