@@ -37,10 +37,11 @@ constexpr int SAMPLE_THREADS = 256;
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_partial_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
                       const long long* __restrict__ request, const int* __restrict__ step,
-                      unsigned long long seed, float* __restrict__ part_v, int* __restrict__ part_i,
-                      int* __restrict__ out, int n_chunks) {
+                      unsigned long long seed, const unsigned long long* __restrict__ seed_ptr,
+                      float* __restrict__ part_v, int* __restrict__ part_i, int* __restrict__ out, int n_chunks) {
     pdl_launch_dependents();
     pdl_wait();
+    if (seed_ptr != nullptr) seed = *seed_ptr;       // a seed kept on the device: a captured graph serves every seed
     const int row = blockIdx.y, chunk = blockIdx.x;
     const float* x = logits + (size_t)row * V;
     const float temp = temperature ? temperature[row] : 0.f;
@@ -135,10 +136,11 @@ extern "C" long long fd_sample_scratch_words(int n, int V) {
 
 // logits [n, V] float; temperature [n] float or null (all greedy); request [n]
 // int64 and step [n] int32 (needed when any temperature is > 0); out [n] int32;
-// scratch: fd_sample_scratch_words(n, V) words (may be null when that is 0).
+// scratch: fd_sample_scratch_words(n, V) words (may be null when that is 0).  seed_ptr (optional): the seed is
+// read from there (device memory) instead of `seed`.
 extern "C" int fd_sample(const float* logits, int n, int V, const float* temperature,
-                         const long long* request, const int* step, unsigned long long seed, int* out,
-                         void* scratch, cudaStream_t stream) {
+                         const long long* request, const int* step, unsigned long long seed,
+                         const unsigned long long* seed_ptr, int* out, void* scratch, cudaStream_t stream) {
     if (n == 0) return 0;
     FD_REQUIRE(V > 0, -2, "sample: vocabulary %d", V);
     FD_REQUIRE(n <= 65535, -2, "sample: %d rows in one call", n);
@@ -149,7 +151,7 @@ extern "C" int fd_sample(const float* logits, int n, int V, const float* tempera
     float* part_v = (float*)scratch;
     int* part_i = (int*)scratch + (size_t)chunks * n;
     dim3 grid(chunks, n);
-    sample_partial_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, request, step, seed,
+    sample_partial_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, request, step, seed, seed_ptr,
                                                              part_v, part_i, out, chunks);
     int rc = check_launch("sample");
     if (rc != 0 || chunks == 1) return rc;
@@ -203,7 +205,7 @@ extern "C" int fd_sample_no_alloc(const float* logits, int n, int V, const float
     int* part_i = static_cast<int*>(g_no_alloc_ptr[dev]) + (size_t)chunks * n;
 
     dim3 grid(chunks, n);
-    sample_partial_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, request, step, seed,
+    sample_partial_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, request, step, seed, nullptr,
                                                              part_v, part_i, out, chunks);
     int rc = check_launch("sample_no_alloc");
     if (rc != 0 || chunks == 1) return rc;

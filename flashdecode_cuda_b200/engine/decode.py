@@ -43,7 +43,8 @@ class _Graph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.ctx: Optional[StepContext] = None
         self.sampled: Optional[torch.Tensor] = None
-        self.temp = self.req = self.step = None
+        self.temp = self.req = self.step = self.seed = None
+        self.seed_value: Optional[int] = None
         self.launches = 0
         self.sample_scratch = None
         self.n_rows_real = 0
@@ -79,7 +80,7 @@ class GraphDecoder:
         while bound < longest:
             bound *= 2
         bound = min(bound, self.cache.max_len)
-        return (bucket_of(n), bound, greedy, seed if not greedy else 0)
+        return (bucket_of(n), bound, greedy, 0)       # the seed lives in device memory: one graph serves every seed
 
     def _prepare(self, g: _Graph, key: Tuple, slots: Sequence[int], tokens: Sequence[int]) -> StepContext:
         B, bound = key[0], key[1]
@@ -92,7 +93,7 @@ class GraphDecoder:
         if key[2]:
             K.sample(logits, g.sampled, scratch=g.sample_scratch)
         else:
-            K.sample(logits, g.sampled, g.temp, g.req, g.step, key[3], scratch=g.sample_scratch)
+            K.sample(logits, g.sampled, g.temp, g.req, g.step, 0, scratch=g.sample_scratch, seed_tensor=g.seed)
 
     def _refill(self, g: _Graph, key: Tuple, slots: Sequence[int], tokens: Sequence[int]) -> None:
         """Re-upload the index array of a captured graph for a new step: the batch-shape parts
@@ -135,6 +136,7 @@ class GraphDecoder:
         g.temp = torch.zeros(B, dtype=torch.float32, device=dev)
         g.req = torch.zeros(B, dtype=torch.int64, device=dev)
         g.step = torch.zeros(B, dtype=torch.int32, device=dev)
+        g.seed = torch.zeros(1, dtype=torch.int64, device=dev)
         g.sample_scratch = torch.zeros(max(1, K.sample_scratch_words(B, self.model.vocab_size)),
                                        dtype=torch.int32, device=dev)
         ctx = self._prepare(g, key, slots, tokens)
@@ -187,6 +189,10 @@ class GraphDecoder:
             g.temp.copy_(torch.tensor(list(temperatures) + [0.0] * pad, dtype=torch.float32), non_blocking=False)
             g.req.copy_(torch.tensor(list(request_ids) + [0] * pad, dtype=torch.int64))
             g.step.copy_(torch.tensor(list(steps) + [0] * pad, dtype=torch.int32))
+            if g.seed_value != seed:
+                bits = seed & 0xFFFFFFFFFFFFFFFF
+                g.seed.fill_(bits - (1 << 64) if bits >= (1 << 63) else bits)       # the same 64 bits, as int64
+                g.seed_value = seed
         g.graph.replay()
         for s in slots:
             cache.advance(s, 1)

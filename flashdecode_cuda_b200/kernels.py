@@ -95,7 +95,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "fd_attention_simt": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P],
         "fd_attention": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P, c_ulonglong, P],
         "fd_attention_mma_sync": [P, P, P, P, I, P, I, I, I, P, P, P, P, P, I, I, I, I, I, I, F, I, I, I, P, P, P, P],
-        "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P],
+        "fd_sample": [P, I, I, P, P, P, c_ulonglong, P, P, P, P],
         "fd_copy_h2d_async": [P, P, LL, P],
         "fd_copy_d2h_sync": [P, P, LL, P],
     }
@@ -538,10 +538,12 @@ def sample_scratch_words(n: int, V: int) -> int:
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            request: Optional[torch.Tensor] = None, step: Optional[torch.Tensor] = None, seed: int = 0,
-           scratch: Optional[torch.Tensor] = None) -> None:
+           scratch: Optional[torch.Tensor] = None, seed_tensor: Optional[torch.Tensor] = None) -> None:
     """out[i] = argmax (greedy) or a Gumbel-max draw from softmax(logits[i] / T_i).
     ``scratch``: int32 tensor of ``sample_scratch_words(n, V)`` entries for large
-    vocabularies; when omitted a per-device buffer is kept and reused."""
+    vocabularies; when omitted a per-device buffer is kept and reused.  ``seed_tensor``:
+    a one-element int64 tensor on the device that holds the seed (its 64 bits) instead of
+    ``seed``, so that a captured graph serves any seed."""
     n, V = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32
     if temperature is not None:
@@ -555,5 +557,7 @@ def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.
             _sample_scratch[key] = scratch
     if words:
         assert scratch.dtype == torch.int32 and scratch.numel() >= words
+    assert seed_tensor is None or (seed_tensor.dtype == torch.int64 and seed_tensor.numel() == 1)
     _check(lib().fd_sample(_ptr(logits), n, V, _ptr(temperature), _ptr(request), _ptr(step),
-                           seed & 0xFFFFFFFFFFFFFFFF, _ptr(out), _ptr(scratch) if words else None, _stream()))
+                           seed & 0xFFFFFFFFFFFFFFFF, _ptr(seed_tensor), _ptr(out), _ptr(scratch) if words else None,
+                           _stream()))

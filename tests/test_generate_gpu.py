@@ -79,6 +79,13 @@ def test_temperature_stop_tokens_and_early_end(folders):
         assert r.tokens == full[:cut]
         assert r.finish_reason == ("stop" if stop in full else "length")
     assert got[0].finish_reason == "stop" and len(got[0].tokens) == 3
+    # another seed, also one beyond 63 bits: other draws, through the graphs captured for the first seed
+    n_graphs = len(eng._decoder().graphs)
+    for seed in (78, (1 << 63) + 5):
+        want2 = [P.generate(raw, w, p, 8, temperature=0.8, seed=seed, request=i) for i, p in enumerate(prompts)]
+        assert [r.tokens for r in eng.generate(prompts, 8, temperature=0.8, seed=seed)] == want2
+        assert want2 != want
+    assert len(eng._decoder().graphs) == n_graphs
     eng.model.check_status()
 
 
