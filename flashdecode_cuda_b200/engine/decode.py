@@ -9,9 +9,11 @@ batch-size bucket and replayed; per step the host only reserves cache blocks,
 uploads one small index array and launches the graph.
 
 A graph is tied to fixed device buffers (its own workspace) and to grid sizes,
-so it is keyed by the padded batch size, a bound on the longest sequence (it
-sizes the split of the keys) and the sampler's constants.  Padding rows carry
-slot -1; every kernel skips them, so padding changes no result.
+so it is keyed by the padded batch size, a bound on the longest sequence (a
+power of two; it sizes the split of the keys) and whether the step samples or
+takes the argmax; temperatures, request ids, step counters and the seed are
+read from device memory.  Padding rows carry slot -1; every kernel skips them,
+so padding changes no result.
 """
 
 from __future__ import annotations
